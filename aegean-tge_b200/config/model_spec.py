@@ -33,14 +33,18 @@ class LayerSpec:
 
     ``cache_from`` names another layer (by its index in ``ModelSpec.layers``)
     whose cache this layer's mixer reads instead of writing one of its own.
+    ``feed_forward`` is None for a layer that has only a mixer, ``ffn_norm`` is
+    None for an arrangement with one norm (both sublayers read its output);
+    ``block_params`` are the arrangement's own constants (a residual multiplier).
     """
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: Optional[PartSpec]
     cache_from: Optional[int] = None
+    block_params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -91,7 +95,9 @@ class ModelSpec:
 def expected_tensors(spec: ModelSpec) -> Dict[str, str]:
     """Checkpoint tensor name -> "where it is used", for error messages."""
     names: Dict[str, str] = {}
-    def add(part: PartSpec, where: str) -> None:
+    def add(part: Optional[PartSpec], where: str) -> None:
+        if part is None:
+            return
         for local, name in part.weights.items():
             names.setdefault(name, f"{where}.{local}")
     add(spec.embedding, "embedding")

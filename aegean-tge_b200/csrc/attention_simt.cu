@@ -10,7 +10,8 @@
 // src/models/qwen2.cpp:1243-1304): kv head = h / group; for t in [first, p]:
 // s_t = dot(q, K_t) * scale (dot first, scale after); softmax over s; out = sum w_t V_t.
 // The causal mask is the loop bound; `window` > 0 additionally drops keys older
-// than p - window + 1.
+// than p - window + 1.  Values may have a size of their own (`value_dim`), and a head may have a sink: a learned
+// score `sink[h]` that joins the softmax's denominator once, unscaled, with no key and no value behind it.
 #include "common.cuh"
 
 namespace {
@@ -22,7 +23,8 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     const int* __restrict__ block_table, int max_pages, int num_pages, int page_size,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, T* __restrict__ out, int out_stride,
-    int heads, int kv_heads, int head_dim, float scale, int window, int* status) {
+    int heads, int kv_heads, int head_dim, int value_dim, const float* __restrict__ sink, float scale, int window,
+    int* status) {
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * 4 + warp;
@@ -50,11 +52,12 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
       break;
     }
     const size_t base = ((size_t)page * kv_heads + kvh) * page_size * head_dim;
+    const size_t vbase = ((size_t)page * kv_heads + kvh) * page_size * value_dim;
     const int lo = max(first - page_index * page_size, 0);
     const int hi = min(pos - page_index * page_size, page_size - 1);
     for (int slot = lo; slot <= hi; ++slot) {
       const T* krow = k_pages + base + (size_t)slot * head_dim;
-      const T* vrow = v_pages + base + (size_t)slot * head_dim;
+      const T* vrow = v_pages + vbase + (size_t)slot * value_dim;
       float dot = 0.0f;
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -70,17 +73,26 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
 #pragma unroll
       for (int i = 0; i < MAX_PER_LANE; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) acc[i] = fmaf(p, to_float<T>(vrow[d]), acc[i] * corr);
+        if (d < value_dim) acc[i] = fmaf(p, to_float<T>(vrow[d]), acc[i] * corr);
       }
       m = m_new;
     }
   }
+  if (sink != nullptr) {
+    // the sink enters like one more key whose value is zero
+    const float s = sink[h];
+    const float m_new = fmaxf(m, s);
+    const float corr = expf(m - m_new);
+    l = l * corr + expf(s - m_new);
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) acc[i] *= corr;
+  }
   const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-  T* orow = out + (size_t)t * out_stride + (size_t)h * head_dim;
+  T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
 #pragma unroll
   for (int i = 0; i < MAX_PER_LANE; ++i) {
     const int d = lane + 32 * i;
-    if (d < head_dim) orow[d] = from_float<T>(acc[i] * inv);
+    if (d < value_dim) orow[d] = from_float<T>(acc[i] * inv);
   }
 }
 
@@ -89,11 +101,13 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
 TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_pages, int num_pages, int page_size,
                                const int* positions, const int* seq_of_token, void* out, int out_stride, int tokens,
-                               int heads, int kv_heads, int head_dim, float scale, int window, int is_bf16,
-                               int* status, cudaStream_t stream) {
+                               int heads, int kv_heads, int head_dim, int value_dim, const float* sink, float scale,
+                               int window, int is_bf16, int* status, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
   TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE, "attention: head_dim %d outside (0, %d]", head_dim,
+              32 * MAX_PER_LANE);
+  TGE_REQUIRE(value_dim > 0 && value_dim <= 32 * MAX_PER_LANE, "attention: value_dim %d outside (0, %d]", value_dim,
               32 * MAX_PER_LANE);
   TGE_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad page geometry");
   TGE_REQUIRE(window >= 0, "attention: negative window");
@@ -103,10 +117,11 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
     attention_simt_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
         max_pages, num_pages, page_size, positions, seq_of_token, (__nv_bfloat16*)out, out_stride, heads, kv_heads,
-        head_dim, scale, window, status);
+        head_dim, value_dim, sink, scale, window, status);
   else
     attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
         (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_pages, num_pages,
-        page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, scale, window, status);
+        page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, sink, scale,
+        window, status);
   return tge_launched("attention_simt", 1);
 }

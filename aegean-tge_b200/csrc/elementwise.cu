@@ -154,21 +154,21 @@ TGE_API int tge_rmsnorm(const float* x, const float* weight, const int* rows, vo
 // x += y  (float32 stream, y in the run dtype)
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void add_to_stream_kernel(float* __restrict__ x, const T* __restrict__ y, size_t count) {
+__global__ void add_to_stream_kernel(float* __restrict__ x, const T* __restrict__ y, size_t count, float alpha) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < count; i += stride) x[i] += to_float<T>(y[i]);
+  for (; i < count; i += stride) x[i] += alpha * to_float<T>(y[i]);
 }
 
-TGE_API int tge_add_to_stream(float* x, const void* y, int y_is_bf16, long long count, cudaStream_t stream) {
+TGE_API int tge_add_to_stream(float* x, const void* y, int y_is_bf16, long long count, float alpha, cudaStream_t stream) {
   TGE_REQUIRE(count >= 0, "add_to_stream: negative count");
   if (count == 0) return 0;
   long long blocks = (count + 255) / 256;
   if (blocks > tge_sm_count() * 16) blocks = tge_sm_count() * 16;
   if (y_is_bf16)
-    add_to_stream_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)y, (size_t)count);
+    add_to_stream_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)y, (size_t)count, alpha);
   else
-    add_to_stream_kernel<float><<<(int)blocks, 256, 0, stream>>>(x, (const float*)y, (size_t)count);
+    add_to_stream_kernel<float><<<(int)blocks, 256, 0, stream>>>(x, (const float*)y, (size_t)count, alpha);
   return tge_launched("add_to_stream", 1);
 }
 
@@ -397,4 +397,163 @@ TGE_API int tge_scale_rows(const void* rows, long long ld_rows, const float* sum
   tge_launch(scale_rows_kernel, m_rows, 256, 0, stream, (const __nv_bfloat16*)rows, ld_rows, sums, slices, width, eps,
              (__nv_bfloat16*)out, ld_out, m_rows, n_cols);
   return tge_launched("scale_rows", 1);
+}
+
+// ---------------------------------------------------------------------------
+// RMS norm of the query and key projections fused with a blend of the values and the cache store: what
+// the rotate-and-store kernel is to a rotary layer, for a layer that normalises q and k instead.
+//   q <- q / sqrt(mean(q^2) + eps) * wq      k <- k / sqrt(mean(k^2) + eps) * wk        (float32 statistics)
+// The mean runs over the WHOLE projection of a token (all heads at once; weights of that size) or, with
+// `per_head`, over each head by itself (weights of one head's size).  A null weight leaves that projection
+// as it is.  With `v_other` the values become (1 - lambda) v + lambda v_other (lambda read from the device,
+// v_other another layer's values of the same tokens); the blended values are what the pages get and what
+// stays in the row.  q, k and v are rewritten in place inside the fused row [q | k | v]; k and v go to their
+// pages, [kv_heads, page_size, head_dim] and [kv_heads, page_size, value_dim].  One block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(
+    T* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    float eps, int per_head, const T* __restrict__ v_other, int v_other_stride, const float* __restrict__ blend,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+    int max_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int page_size, int heads,
+    int kv_heads, int head_dim, int value_dim, int store_kv, int* status) {
+  __shared__ float scratch[32];
+  __shared__ float head_factor[256];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int seq = seq_of_token[t];
+  const float lambda = blend != nullptr ? blend[0] : 0.0f;            // a model constant: not the previous kernel's work
+  pdl_wait();
+  T* row = qkv + (size_t)t * row_stride;
+  T* k_row = row + (size_t)heads * head_dim;
+  T* v_row = k_row + (size_t)kv_heads * head_dim;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+
+  size_t k_base = 0, v_base = 0;
+  bool store = store_kv != 0;
+  if (store) {
+    const int page_index = pos / page_size;
+    const int page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+      store = false;
+    } else {
+      k_base = ((size_t)page * kv_heads * page_size + (pos % page_size)) * head_dim;
+      v_base = ((size_t)page * kv_heads * page_size + (pos % page_size)) * value_dim;
+    }
+  }
+
+  // the two projections, one after the other: which == 0 queries, which == 1 keys
+  for (int which = 0; which < 2; ++which) {
+    T* base = which == 0 ? row : k_row;
+    const float* weight = which == 0 ? q_weight : k_weight;
+    const int count = (which == 0 ? heads : kv_heads);
+    const int width = count * head_dim;
+    if (weight != nullptr) {
+      if (per_head) {
+        for (int h0 = 0; h0 < count; h0 += 256) {
+          for (int h = h0 + warp; h < min(count, h0 + 256); h += warps) {
+            float sum = 0.0f;
+            for (int d = lane; d < head_dim; d += 32) {
+              const float v = to_float<T>(base[(size_t)h * head_dim + d]);
+              sum = fmaf(v, v, sum);
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) head_factor[h - h0] = 1.0f / sqrtf(sum / (float)head_dim + eps);
+          }
+          __syncthreads();
+          for (int i = h0 * head_dim + threadIdx.x; i < min(count, h0 + 256) * head_dim; i += blockDim.x) {
+            const int h = i / head_dim;
+            base[i] = from_float<T>(to_float<T>(base[i]) * head_factor[h - h0] * weight[i - h * head_dim]);
+          }
+          __syncthreads();
+        }
+      } else {
+        float sum = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+          const float v = to_float<T>(base[i]);
+          sum = fmaf(v, v, sum);
+        }
+        const float factor = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps);
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+          base[i] = from_float<T>(to_float<T>(base[i]) * factor * weight[i]);
+      }
+    }
+    if (which == 1 && store) {
+      // every thread stores the elements it has just written itself
+      const int step = (weight != nullptr && per_head) ? 0 : 1;
+      if (step == 0) __syncthreads();
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        k_pages[k_base + (size_t)h * page_size * head_dim + d] = k_row[i];
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+    T v = v_row[i];
+    if (v_other != nullptr) {
+      const float mine = to_float<T>(v), other = to_float<T>(v_other[(size_t)t * v_other_stride + i]);
+      v = from_float<T>((1.0f - lambda) * mine + lambda * other);
+      v_row[i] = v;
+    }
+    if (store) {
+      const int h = i / value_dim, d = i - h * value_dim;
+      v_pages[v_base + (size_t)h * page_size * value_dim + d] = v;
+    }
+  }
+}
+
+// qkv: [tokens, >= heads*head_dim + kv_heads*(head_dim + value_dim)] rows of [q | k | v], row stride in elements.
+// q_weight / k_weight: float32, heads*head_dim and kv_heads*head_dim long (or head_dim each with per_head), or null.
+// v_other: null, or the other layer's values [tokens, kv_heads*value_dim] with its row stride; blend: device float.
+TGE_API int tge_qk_norm_kv_store(void* qkv, int is_bf16, int row_stride, const float* q_weight, const float* k_weight,
+                                 float eps, int per_head, const void* v_other, int v_other_stride, const float* blend,
+                                 const int* positions, const int* seq_of_token, const int* block_table, int max_pages,
+                                 void* k_pages, void* v_pages, int num_pages, int page_size, int tokens, int heads,
+                                 int kv_heads, int head_dim, int value_dim, int store_kv, int* status,
+                                 cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && head_dim > 0 && value_dim > 0, "qk_norm_kv_store: bad sizes");
+  TGE_REQUIRE(row_stride >= heads * head_dim + kv_heads * (head_dim + value_dim), "qk_norm_kv_store: rows of %d elements "
+              "do not hold q, k and v", row_stride);
+  TGE_REQUIRE(eps > 0.0f || (q_weight == nullptr && k_weight == nullptr), "qk_norm_kv_store: eps must be positive");
+  TGE_REQUIRE((v_other == nullptr) == (blend == nullptr), "qk_norm_kv_store: a blend needs both the other values and lambda");
+  TGE_REQUIRE(!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0 && k_pages && v_pages && block_table),
+              "qk_norm_kv_store: bad page geometry");
+  if (tokens == 0) return 0;
+  if (is_bf16)
+    tge_launch(qk_norm_kv_store_kernel<__nv_bfloat16>, tokens, 256, 0, stream, (__nv_bfloat16*)qkv, row_stride, q_weight,
+               k_weight, eps, per_head, (const __nv_bfloat16*)v_other, v_other_stride, blend, positions, seq_of_token,
+               block_table, max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads,
+               kv_heads, head_dim, value_dim, store_kv, status);
+  else
+    tge_launch(qk_norm_kv_store_kernel<float>, tokens, 256, 0, stream, (float*)qkv, row_stride, q_weight, k_weight, eps,
+               per_head, (const float*)v_other, v_other_stride, blend, positions, seq_of_token, block_table, max_pages,
+               (float*)k_pages, (float*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, value_dim, store_kv,
+               status);
+  return tge_launched("qk_norm_kv_store", 1);
+}
+
+// ---------------------------------------------------------------------------
+// Soft cap of float32 scores, in place: z <- cap * tanh(z / cap).
+// ---------------------------------------------------------------------------
+__global__ void soft_cap_kernel(float* __restrict__ z, long long ld, int rows, int cols, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t count = (size_t)rows * cols;
+  const float inv = 1.0f / cap;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols, c = i - r * cols;
+    float* at = z + r * ld + c;
+    *at = cap * tanhf(*at * inv);
+  }
+}
+
+TGE_API int tge_soft_cap(float* z, long long ld, int rows, int cols, float cap, cudaStream_t stream) {
+  TGE_REQUIRE(rows >= 0 && cols > 0 && ld >= cols && cap > 0.0f, "soft_cap: bad arguments");
+  if (rows == 0) return 0;
+  long long blocks = ((long long)rows * cols + 255) / 256;
+  if (blocks > tge_sm_count() * 8) blocks = tge_sm_count() * 8;
+  tge_launch(soft_cap_kernel, (int)blocks, 256, 0, stream, z, ld, rows, cols, cap);
+  return tge_launched("soft_cap", 1);
 }

@@ -16,7 +16,11 @@ enum GemmEpilogue : int {
   GEMM_STORE_F32 = 1,  // out[m, n] = acc + bias[n], float32
   GEMM_ADD_F32 = 2,    // residual[m, n] += acc + bias[n], float32 in place
   GEMM_SWIGLU = 3,     // w rows interleaved (gate_i, up_i): out[m, i] = silu(g) * u, run dtype
+  GEMM_GELU = 4,       // out[m, n] = gelu(acc + bias[n]) for n >= act_from (plain below it), run dtype; the erf form
+  GEMM_GELU_TANH = 5,  // the same with the tanh approximation 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
 };
+// `alpha` multiplies acc + bias in the three plain epilogues (store, store float32, add): a residual multiplier or a
+// logit scale costs no pass of its own.
 
 namespace {
 
@@ -56,7 +60,8 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* base, 
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ x, size_t ldx, const T* __restrict__ w,
                                                         size_t ldw, const float* __restrict__ bias, void* out,
-                                                        size_t ldo, int M, int N, int K, int epilogue, int vec) {
+                                                        size_t ldo, int M, int N, int K, int epilogue, int vec,
+                                                        float alpha, int act_from) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -116,6 +121,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ x,
       if (n >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[n];
+      if (epilogue >= GEMM_GELU) {
+        if (n >= act_from) v = epilogue == GEMM_GELU ? gelu_erf(v) : gelu_tanh(v);
+        reinterpret_cast<T*>(out)[(size_t)m * ldo + n] = from_float<T>(v);
+        continue;
+      }
+      v *= alpha;
       if (epilogue == GEMM_STORE) {
         reinterpret_cast<T*>(out)[(size_t)m * ldo + n] = from_float<T>(v);
       } else if (epilogue == GEMM_STORE_F32) {
@@ -132,9 +143,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ x,
 // x [M, K] (row stride ldx), w [N, K] (row stride ldw), both in the run dtype;
 // bias float32 [N] or null; out as the epilogue says (row stride ldo, in elements).
 TGE_API int tge_gemm_simt(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
-                          long long ldo, int M, int N, int K, int is_bf16, int epilogue, cudaStream_t stream) {
+                          long long ldo, int M, int N, int K, int is_bf16, int epilogue, float alpha, int act_from,
+                          cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
   TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
   TGE_REQUIRE(ldx >= K && ldw >= K, "gemm: row strides %lld/%lld shorter than K=%d", ldx, ldw, K);
   if (M == 0) return 0;
@@ -146,9 +158,9 @@ TGE_API int tge_gemm_simt(const void* x, long long ldx, const void* w, long long
   if (is_bf16)
     gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)x, (size_t)ldx,
                                                               (const __nv_bfloat16*)w, (size_t)ldw, bias, out,
-                                                              (size_t)ldo, M, N, K, epilogue, vec);
+                                                              (size_t)ldo, M, N, K, epilogue, vec, alpha, act_from);
   else
     gemm_simt_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, (size_t)ldx, (const float*)w, (size_t)ldw,
-                                                      bias, out, (size_t)ldo, M, N, K, epilogue, vec);
+                                                      bias, out, (size_t)ldo, M, N, K, epilogue, vec, alpha, act_from);
   return tge_launched("gemm_simt", 1);
 }

@@ -30,7 +30,11 @@
 
 #include "common.cuh"
 
-enum GemmEpilogue : int { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_SWIGLU = 3 };
+enum GemmEpilogue : int { GEMM_STORE = 0, GEMM_STORE_F32 = 1, GEMM_ADD_F32 = 2, GEMM_SWIGLU = 3, GEMM_GELU = 4,
+                          GEMM_GELU_TANH = 5 };
+// GEMM_GELU / GEMM_GELU_TANH: bfloat16 out = gelu(acc + bias) in the erf or the tanh form for weight rows n >= act_from,
+// plain acc + bias below (a product over row-concatenated weights may activate only its tail).  `alpha` multiplies
+// acc + bias in the store, store-float32 and add epilogues.
 
 namespace {
 
@@ -60,6 +64,8 @@ struct GemmParams {
   const float* ss;
   int ss_slices, ss_width;
   float ss_eps;
+  float alpha;         // multiplies acc + bias in the plain epilogues (1: none)
+  int act_from;        // first weight row the GELU epilogues activate
 };
 constexpr int DEFER_MAX_TOKENS = 128;
 
@@ -196,7 +202,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       for (int j = 0; j < 16; ++j) old[j] = (n_ok && m0 + j < p.m_tok) ? dst[(size_t)j * p.ldo] : 0.0f;
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + __uint_as_float(r[j]) + bias;
+        if (n_ok && m0 + j < p.m_tok) dst[(size_t)j * p.ldo] = old[j] + p.alpha * (__uint_as_float(r[j]) + bias);
       continue;
     }
     if (!p.to_partial && p.epilogue == GEMM_SWIGLU) {
@@ -222,8 +228,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       if (p.to_partial) {
         if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
       } else if (n_ok && m < p.m_tok) {
-        if (p.epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
-        else reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = v;
+        if (p.epilogue >= GEMM_GELU) {
+          if (n >= p.act_from) v = p.epilogue == GEMM_GELU ? gelu_erf(v) : gelu_tanh(v);
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
+        } else if (p.epilogue == GEMM_STORE) {
+          reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(p.alpha * v);
+        } else {
+          reinterpret_cast<float*>(p.out)[(size_t)m * p.ldo + n] = p.alpha * v;
+        }
       }
     }
   }
@@ -615,7 +627,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid
 // Adds the k-splits in split order and applies the epilogue.
 __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const float* __restrict__ bias, void* out,
                                        long long ldo, int m_tok, int n_w, int splits, int epilogue,
-                                       const float* __restrict__ ss, int ss_slices, int ss_width, float ss_eps) {
+                                       const float* __restrict__ ss, int ss_slices, int ss_width, float ss_eps,
+                                       float alpha, int act_from) {
   pdl_trigger();
   pdl_wait();
   const size_t plane = (size_t)m_tok * n_w;
@@ -643,6 +656,12 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
     for (int s = 0; s < splits; ++s) v += partial[s * plane + i];
     v *= row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, m);
     if (bias) v += bias[n];
+    if (epilogue >= GEMM_GELU) {
+      if (n >= act_from) v = epilogue == GEMM_GELU ? gelu_erf(v) : gelu_tanh(v);
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+      continue;
+    }
+    v *= alpha;
     if (epilogue == GEMM_STORE) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
     else if (epilogue == GEMM_STORE_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
     else reinterpret_cast<float*>(out)[(size_t)m * ldo + n] += v;
@@ -940,7 +959,7 @@ namespace {
 int launch_product(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                    long long ldo, int M, int N, int K, int epilogue, float* scratch, long long scratch_floats,
                    int force_bn, int force_splits, bool partial_always, int* status, cudaStream_t stream,
-                   int* splits_out, const RowSums& sums = RowSums()) {
+                   int* splits_out, const RowSums& sums = RowSums(), float alpha = 1.0f, int act_from = 0) {
   if (K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || (uintptr_t)x % 16 != 0 || (uintptr_t)w % 16 != 0) return TGE_UNSUPPORTED;
   if (scratch == nullptr) scratch_floats = 0;
   const Plan plan = make_plan(M, N, K, scratch_floats, force_bn, force_splits);
@@ -976,6 +995,7 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
     p.to_partial = pair_partial ? 1 : 0;
     p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
     p.ss = nullptr; p.ss_slices = 0; p.ss_width = 0; p.ss_eps = 0.0f;
+    p.alpha = alpha; p.act_from = act_from;
     const size_t smem = 1024 + (size_t)pair_plan.stages * (A_STAGE_BYTES + (pair_plan.bn / 2) * BK * 2) +
                         8 * (2 * pair_plan.stages + 4) + 16;
     const long long total = (long long)p.tiles_w * p.tiles_t * p.splits;
@@ -1004,6 +1024,7 @@ int launch_product(const void* x, long long ldx, const void* w, long long ldw, c
   p.to_partial = to_partial ? 1 : 0;
   p.bias = bias; p.out = out; p.ldo = ldo; p.partial = scratch; p.status = status;
   p.ss = sums.ss; p.ss_slices = sums.slices; p.ss_width = sums.width; p.ss_eps = sums.eps;
+  p.alpha = alpha; p.act_from = act_from;
 
   const size_t smem = 1024 + (size_t)plan.stages * (A_STAGE_BYTES + plan.bn * BK * 2) + 8 * (2 * plan.stages + 4) + 16 +
                       DEFER_MAX_TOKENS * sizeof(float);
@@ -1035,7 +1056,8 @@ constexpr int NORM_PER_THREAD = 8;               // columns per thread: rows up 
 __global__ void __launch_bounds__(NORM_THREADS)
 splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ stream,
                        long long ld_stream, const float* __restrict__ norm_weight, float eps,
-                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w, int splits) {
+                       __nv_bfloat16* __restrict__ norm_out, long long ld_norm, int m_tok, int n_w, int splits,
+                       float alpha) {
   __shared__ float scratch[32];
   pdl_trigger();
   const int t = blockIdx.x;
@@ -1059,7 +1081,7 @@ splitk_add_norm_kernel(const float* __restrict__ partial, const float* __restric
       float acc = 0.0f;
 #pragma unroll 4
       for (int s = 0; s < splits; ++s) acc += src[s * plane];
-      const float v = stream[(size_t)t * ld_stream + n] + (acc + add[i]);
+      const float v = stream[(size_t)t * ld_stream + n] + alpha * (acc + add[i]);
       stream[(size_t)t * ld_stream + n] = v;
       value[i] = v;
       sum = fmaf(v, v, sum);
@@ -1177,7 +1199,7 @@ constexpr int SCALE_SLICE = 256;
 __global__ void __launch_bounds__(SCALE_SLICE)
 splitk_add_scale_kernel(const float* __restrict__ partial, const float* __restrict__ bias, float* __restrict__ stream,
                         long long ld_stream, const float* __restrict__ norm_weight, __nv_bfloat16* __restrict__ scaled_out,
-                        long long ld_scaled, float* __restrict__ ss_out, int m_tok, int n_w, int splits) {
+                        long long ld_scaled, float* __restrict__ ss_out, int m_tok, int n_w, int splits, float alpha) {
   __shared__ float scratch[32];
   pdl_trigger();
   const int t = blockIdx.y, n = blockIdx.x * SCALE_SLICE + threadIdx.x;
@@ -1192,7 +1214,7 @@ splitk_add_scale_kernel(const float* __restrict__ partial, const float* __restri
     float acc = 0.0f;
 #pragma unroll 4
     for (int s = 0; s < splits; ++s) acc += src[s * plane];
-    v = stream[(size_t)t * ld_stream + n] + (acc + add);
+    v = stream[(size_t)t * ld_stream + n] + alpha * (acc + add);
     stream[(size_t)t * ld_stream + n] = v;
     scaled_out[(size_t)t * ld_scaled + n] = __float2bfloat16_rn(v * gain);
   }
@@ -1214,9 +1236,10 @@ constexpr int FUSED_MAX_TOKENS = 256;   // above this the product's own epilogue
 TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
                              long long ldo, int M, int N, int K, int epilogue, float* scratch,
                              long long scratch_floats, int force_bn, int force_splits, int* status,
-                             const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps, cudaStream_t stream) {
+                             const float* x_ss, int x_ss_slices, int x_ss_width, float x_ss_eps, float alpha,
+                             int act_from, cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
-  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_SWIGLU, "gemm: unknown epilogue %d", epilogue);
+  TGE_REQUIRE(epilogue >= GEMM_STORE && epilogue <= GEMM_GELU_TANH, "gemm: unknown epilogue %d", epilogue);
   TGE_REQUIRE(epilogue != GEMM_SWIGLU || N % 2 == 0, "gemm: the gated epilogue needs an even number of weight rows, got %d", N);
   TGE_REQUIRE(force_bn == 0 || (force_bn % 16 == 0 && force_bn >= 16 && force_bn <= 256), "gemm: token tile %d must be a multiple of 16 in [16, 256]", force_bn);
   TGE_REQUIRE(status != nullptr, "gemm_tcgen05: needs a status word");
@@ -1225,14 +1248,14 @@ TGE_API int tge_gemm_tcgen05(const void* x, long long ldx, const void* w, long l
   RowSums sums;
   sums.ss = x_ss; sums.slices = x_ss_slices; sums.width = x_ss_width; sums.eps = x_ss_eps;
   int rc = launch_product(x, ldx, w, ldw, bias, out, ldo, M, N, K, epilogue, scratch, scratch_floats, force_bn,
-                          force_splits, false, status, stream, &splits, sums);
+                          force_splits, false, status, stream, &splits, sums, alpha, act_from);
   if (rc != 1) return rc;
   if (splits > 0) {
     const long long count = epilogue == GEMM_SWIGLU ? (long long)M * N / 2 : (long long)M * N;
     long long blocks = (count + 255) / 256;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     tge_launch(splitk_epilogue_kernel, (int)blocks, 256, 0, stream, (const float*)scratch, bias, out, ldo, M, N, splits,
-               epilogue, x_ss, x_ss_slices, x_ss_width, x_ss_eps);
+               epilogue, x_ss, x_ss_slices, x_ss_width, x_ss_eps, alpha, act_from);
     return tge_launched("splitk_epilogue", 2);
   }
   return 1;
@@ -1246,7 +1269,7 @@ TGE_API int tge_gemm_tcgen05_defer_slices(int N) { return (N + SCALE_SLICE - 1) 
 TGE_API int tge_gemm_tcgen05_add_defer(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
                                        float* stream_out, long long ldo, int M, int N, int K, const float* norm_weight,
                                        void* scaled_out, long long ld_scaled, float* ss_out, float* scratch,
-                                       long long scratch_floats, int* status, cudaStream_t stream) {
+                                       long long scratch_floats, int* status, float alpha, cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+defer: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(status != nullptr && norm_weight != nullptr && scaled_out != nullptr && ss_out != nullptr, "gemm+defer: bad arguments");
   if (M == 0) return 0;
@@ -1257,7 +1280,7 @@ TGE_API int tge_gemm_tcgen05_add_defer(const void* x, long long ldx, const void*
   if (rc != 1) return rc;
   tge_launch(splitk_add_scale_kernel, dim3((N + SCALE_SLICE - 1) / SCALE_SLICE, M), SCALE_SLICE, 0, stream,
              (const float*)scratch, bias, stream_out, ldo, norm_weight, (__nv_bfloat16*)scaled_out, ld_scaled, ss_out, M, N,
-             splits);
+             splits, alpha);
   return tge_launched("splitk_add_scale", 2);
 }
 
@@ -1268,7 +1291,7 @@ TGE_API int tge_gemm_tcgen05_add_defer(const void* x, long long ldx, const void*
 TGE_API int tge_gemm_tcgen05_add_norm(const void* x, long long ldx, const void* w, long long ldw, const float* bias,
                                       float* stream_out, long long ldo, int M, int N, int K, const float* norm_weight,
                                       float eps, void* norm_out, long long ld_norm, float* scratch,
-                                      long long scratch_floats, int* status, cudaStream_t stream) {
+                                      long long scratch_floats, int* status, float alpha, cudaStream_t stream) {
   TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+norm: bad sizes M=%d N=%d K=%d", M, N, K);
   TGE_REQUIRE(status != nullptr && norm_weight != nullptr && norm_out != nullptr && eps > 0.0f, "gemm+norm: bad arguments");
   if (M == 0) return 0;
@@ -1279,7 +1302,7 @@ TGE_API int tge_gemm_tcgen05_add_norm(const void* x, long long ldx, const void* 
   if (rc != 1) return rc;
   tge_launch(splitk_add_norm_kernel, dim3(M), NORM_THREADS, 0, stream,
              (const float*)scratch, bias, stream_out, ldo, norm_weight, eps, (__nv_bfloat16*)norm_out, ld_norm, M, N,
-             splits);
+             splits, alpha);
   return tge_launched("splitk_add_norm", 2);
 }
 

@@ -31,10 +31,14 @@ class DecoderModel:
         self.blocks: List[Block] = []
         for layer in spec.layers:
             mixer = build_part(MIXERS, layer.mixer, env)
-            ffn = build_part(FEED_FORWARDS, layer.feed_forward, env)
+            ffn = build_part(FEED_FORWARDS, layer.feed_forward, env) if layer.feed_forward is not None else None
             norm1 = build_part(NORMS, layer.mixer_norm, env)
-            norm2 = build_part(NORMS, layer.ffn_norm, env)
-            self.blocks.append(BLOCKS.get(layer.block)(mixer, ffn, norm1, norm2, env))
+            norm2 = build_part(NORMS, layer.ffn_norm, env) if layer.ffn_norm is not None else None
+            block_class = BLOCKS.get(layer.block)
+            if layer.block_params:
+                self.blocks.append(block_class(mixer, ffn, norm1, norm2, env, params=dict(layer.block_params)))
+            else:
+                self.blocks.append(block_class(mixer, ffn, norm1, norm2, env))
         self.layer_caches: List[LayerCache] = [LayerCache() for _ in spec.layers]
         # single-token steps may be replayed from a CUDA graph only if every part says so
         self.graph_safe = all(part.graph_safe for _where, part, _spec in self.named_parts())
@@ -47,8 +51,10 @@ class DecoderModel:
         for index, (block, layer) in enumerate(zip(self.blocks, self.spec.layers)):
             out.append((f"layers[{index}].mixer_norm", block.mixer_norm, layer.mixer_norm))
             out.append((f"layers[{index}].mixer", block.mixer, layer.mixer))
-            out.append((f"layers[{index}].ffn_norm", block.ffn_norm, layer.ffn_norm))
-            out.append((f"layers[{index}].feed_forward", block.feed_forward, layer.feed_forward))
+            if block.ffn_norm is not None:
+                out.append((f"layers[{index}].ffn_norm", block.ffn_norm, layer.ffn_norm))
+            if block.feed_forward is not None:
+                out.append((f"layers[{index}].feed_forward", block.feed_forward, layer.feed_forward))
         return out
 
     def manifest(self) -> Dict[str, Tuple[ParamSpec, str]]:
@@ -77,6 +83,8 @@ class DecoderModel:
                     raise KeyError(f"{where}.{local}: tensor '{name}' was not loaded")
             if mine or part.param_specs():
                 part.load(mine)
+        for block in self.blocks:
+            block.loaded()
 
     def step_param_bytes(self) -> int:
         """Bytes of parameters one step reads: every part once per visit, the embedding rows not counted."""

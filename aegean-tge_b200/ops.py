@@ -17,7 +17,7 @@ import torch
 
 from .csrc import build as _build
 
-GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU = 0, 1, 2, 3
+GEMM_STORE, GEMM_STORE_F32, GEMM_ADD_F32, GEMM_SWIGLU, GEMM_GELU, GEMM_GELU_TANH = 0, 1, 2, 3, 4, 5
 STATUS_BITS = {1: "a token id outside the vocabulary", 2: "a page id outside the pool",
                4: "a row index outside the batch", 8: "a bounded device-side wait gave up"}
 
@@ -59,24 +59,24 @@ def core() -> ctypes.CDLL:
         _declare(lib, "tge_embedding", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_rmsnorm", [_c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float,
                                       _c_ptr, _c_ptr])
-        _declare(lib, "tge_add_to_stream", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
+        _declare(lib, "tge_add_to_stream", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_float, _c_ptr])
         _declare(lib, "tge_rope_kv_store", [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                             _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                             _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_gemm_simt", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
-                                        _c_int, _c_int, _c_ptr])
+                                        _c_int, _c_int, _c_float, _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                            _c_int, _c_int, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ptr, _c_int,
-                                           _c_int, _c_float, _c_ptr])
+                                           _c_int, _c_float, _c_float, _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_add_defer", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int,
                                                      _c_int, _c_int, _c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll,
-                                                     _c_ptr, _c_ptr])
+                                                     _c_ptr, _c_float, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_defer_slices", [_c_int])
         _declare(lib, "tge_scale_rows", [_c_ptr, _c_ll, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ll, _c_int,
                                          _c_int, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_add_norm", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                                     _c_int, _c_ptr, _c_float, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr,
-                                                    _c_ptr])
+                                                    _c_float, _c_ptr])
         _declare(lib, "tge_gemm_tcgen05_qkv_rope", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -86,8 +86,12 @@ def core() -> ctypes.CDLL:
         lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_gemm_tcgen05_scratch_floats.restype = _c_ll
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
-                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                             _c_int, _c_int, _c_ptr, _c_ptr])
+                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                             _c_float, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_qk_norm_kv_store", [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_int, _c_ptr, _c_int,
+                                               _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
+                                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_soft_cap", [_c_ptr, _c_ll, _c_int, _c_int, _c_float, _c_ptr])
         _declare(lib, "tge_sample", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_apply_penalty", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
         _declare(lib, "tge_sample_cuts", [_c_ptr, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
@@ -275,14 +279,15 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     return out
 
 
-def add_to_stream(x: torch.Tensor, y: torch.Tensor) -> None:
-    """x (float32) += y (run dtype), same shape."""
+def add_to_stream(x: torch.Tensor, y: torch.Tensor, alpha: float = 1.0) -> None:
+    """x (float32) += alpha * y (run dtype), same shape."""
     _want(x, "stream", torch.float32)
     _want(y, "addend", _FLOAT)
     if x.shape != y.shape:
         raise KernelError(f"add_to_stream: shapes differ, {tuple(x.shape)} and {tuple(y.shape)}")
     lib = core()
-    _check(lib.tge_add_to_stream(x.data_ptr(), y.data_ptr(), int(y.dtype == torch.bfloat16), x.numel(), _stream()), lib)
+    _check(lib.tge_add_to_stream(x.data_ptr(), y.data_ptr(), int(y.dtype == torch.bfloat16), x.numel(), float(alpha),
+                                 _stream()), lib)
 
 
 def rope_kv_store(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary: int,
@@ -321,6 +326,67 @@ def rope_kv_store(qkv: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[
                                  _ptr(block_table), max_pages, _ptr(k_pages), _ptr(v_pages), num_pages, page_size,
                                  tokens, heads, kv_heads if store else 0, head_dim, rotary, int(store),
                                  status_word().data_ptr(), _stream()), lib)
+
+
+def qk_norm_kv_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                     per_head: bool, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                     block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+                     v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, head_dim: int, value_dim: int,
+                     v_other: Optional[torch.Tensor] = None, blend: Optional[torch.Tensor] = None) -> None:
+    """RMS norm of the q and k projections (float32 statistics), an optional blend of the values with another
+    layer's, and the store of k and v into their pages, all in place on the fused rows ``qkv`` [T, q | k | v].
+
+    The norm runs over a token's whole projection (weights float32 [heads*head_dim] and [kv_heads*head_dim]) or,
+    with ``per_head``, over each head (weights [head_dim]); a weight of None leaves that projection alone.
+    ``v_other`` [T, kv_heads*value_dim] (dense rows, any row stride) and ``blend`` (a float32 scalar on the
+    device): v <- (1 - blend) v + blend v_other before the store.  Pages None: nothing is stored.
+    """
+    _want(qkv, "qkv", _FLOAT, contiguous=False)
+    stride = _rows_2d(qkv, "qkv")
+    tokens = qkv.shape[0]
+    for name, t, n in (("q norm weight", q_weight, heads), ("k norm weight", k_weight, kv_heads)):
+        if t is not None:
+            _want(t, name, torch.float32)
+            if t.numel() != (head_dim if per_head else n * head_dim):
+                raise KernelError(f"{name} has {t.numel()} elements")
+    _want(positions, "positions", torch.int32)
+    _want(seq_of_token, "seq_of_token", torch.int32)
+    if (v_other is None) != (blend is None):
+        raise KernelError("qk_norm_kv_store: a blend needs the other values and its weight")
+    other_stride = 0
+    if v_other is not None:
+        _want(v_other, "other values", qkv.dtype, contiguous=False)
+        _want(blend, "blend weight", torch.float32)
+        other_stride = _rows_2d(v_other, "other values")
+        if tuple(v_other.shape) != (tokens, kv_heads * value_dim) or blend.numel() != 1:
+            raise KernelError(f"other values must be [{tokens}, {kv_heads * value_dim}], got {tuple(v_other.shape)}")
+    store = k_pages is not None
+    num_pages = page_size = max_pages = 0
+    if store:
+        _want(k_pages, "k pages", qkv.dtype)
+        _want(v_pages, "v pages", qkv.dtype)
+        _want(block_table, "block table", torch.int32)
+        num_pages, _, page_size, _ = k_pages.shape
+        if (tuple(k_pages.shape) != (num_pages, kv_heads, page_size, head_dim)
+                or tuple(v_pages.shape) != (num_pages, kv_heads, page_size, value_dim)):
+            raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim} | {value_dim}], got "
+                              f"{tuple(k_pages.shape)} and {tuple(v_pages.shape)}")
+        max_pages = block_table.shape[1]
+    lib = core()
+    _check(lib.tge_qk_norm_kv_store(qkv.data_ptr(), int(qkv.dtype == torch.bfloat16), stride, _ptr(q_weight),
+                                    _ptr(k_weight), float(eps), int(per_head), _ptr(v_other), other_stride, _ptr(blend),
+                                    positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table), max_pages,
+                                    _ptr(k_pages), _ptr(v_pages), num_pages, page_size, tokens, heads, kv_heads,
+                                    head_dim, value_dim, int(store), status_word().data_ptr(), _stream()), lib)
+
+
+def soft_cap(z: torch.Tensor, cap: float) -> torch.Tensor:
+    """z (float32 [R, V], dense rows) <- cap * tanh(z / cap), in place."""
+    _want(z, "scores", torch.float32, contiguous=False)
+    ld = _rows_2d(z, "scores")
+    lib = core()
+    _check(lib.tge_soft_cap(z.data_ptr(), ld, z.shape[0], z.shape[1], float(cap), _stream()), lib)
+    return z
 
 
 DEFER_MAX_TOKENS = 128      # rows that may travel without their norm factor (the small-batch products)
@@ -366,13 +432,16 @@ _NO_FACTOR = (None, 0, 0, 0.0)
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
            out: Optional[torch.Tensor] = None, force_simt: bool = False, force_bn: int = 0,
-           force_splits: int = 0) -> torch.Tensor:
+           force_splits: int = 0, alpha: float = 1.0, act_from: int = 0) -> torch.Tensor:
     """out = x . w^T with an epilogue.
 
     x [M, K] and w [N, K] in the run dtype; bias float32 [N] or None.
     GEMM_STORE: out [M, N] run dtype.  GEMM_STORE_F32: out [M, N] float32.
     GEMM_ADD_F32: ``out`` (float32 [M, N], required) += product.
     GEMM_SWIGLU: w rows interleaved (gate_i, up_i); out [M, N/2] run dtype.
+    GEMM_GELU / GEMM_GELU_TANH: out [M, N] run dtype = gelu(product + bias) in the erf / the tanh form for the
+    columns from ``act_from`` on, the plain product below (for row-concatenated weights).
+    ``alpha`` multiplies product + bias in the store and add epilogues (a residual multiplier, a logit scale).
     bfloat16 goes to the tcgen05 kernel when the shape allows TMA, else (and all of
     float32) to the CUDA-core kernel.
     """
@@ -398,7 +467,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
         want_shape, want_dtype = (M, N), torch.float32
     elif epilogue == GEMM_SWIGLU:
         want_shape, want_dtype = (M, N // 2), x.dtype
-    elif epilogue == GEMM_STORE:
+    elif epilogue in (GEMM_STORE, GEMM_GELU, GEMM_GELU_TANH):
         want_shape, want_dtype = (M, N), x.dtype
     else:
         raise KernelError(f"linear: unknown epilogue {epilogue}")
@@ -415,14 +484,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilo
         factor = _NO_FACTOR if deferred is None else deferred.factor_args()
         rc = lib.tge_gemm_tcgen05(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
                                   epilogue, _ptr(scratch), 0 if scratch is None else scratch.numel(), force_bn,
-                                  force_splits, status_word().data_ptr(), *factor, _stream())
+                                  force_splits, status_word().data_ptr(), *factor, float(alpha), int(act_from), _stream())
         if _check(rc, lib) != UNSUPPORTED:
             return out
     if deferred is not None:
         x = deferred.complete()
         ldx = _rows_2d(x, "linear input")
     _check(lib.tge_gemm_simt(x.data_ptr(), ldx, w.data_ptr(), ldw, _ptr(bias), out.data_ptr(), ldo, M, N, K,
-                             int(x.dtype == torch.bfloat16), epilogue, _stream()), lib)
+                             int(x.dtype == torch.bfloat16), epilogue, float(alpha), int(act_from), _stream()), lib)
     return out
 
 
@@ -440,8 +509,9 @@ FUSED_MAX_TOKENS = 144
 
 
 def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], stream: torch.Tensor,
-                    norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype, defer: bool = False):
-    """stream (float32 [M, N]) += x . w^T (+ bias); returns RMSNorm(stream) * norm_weight in ``out_dtype``.
+                    norm_weight: torch.Tensor, eps: float, out_dtype: torch.dtype, defer: bool = False,
+                    alpha: float = 1.0):
+    """stream (float32 [M, N]) += alpha * (x . w^T (+ bias)); returns RMSNorm(stream) * norm_weight in ``out_dtype``.
 
     For a small bfloat16 batch the partial sums of the product are added into the stream and the new
     rows normalised by one kernel; otherwise the product and the norm run as separate kernels.
@@ -470,17 +540,17 @@ def linear_add_norm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tenso
                                                 _rows_2d(w, "linear weight"), _ptr(bias), stream.data_ptr(),
                                                 _rows_2d(stream, "stream"), M, N, K, norm_weight.data_ptr(),
                                                 out.data_ptr(), N, sums.data_ptr(), scratch.data_ptr(),
-                                                scratch.numel(), status_word().data_ptr(), _stream())
+                                                scratch.numel(), status_word().data_ptr(), float(alpha), _stream())
             if _check(rc, lib) != UNSUPPORTED:
                 return DeferredRows(out, sums, N, eps)
         rc = lib.tge_gemm_tcgen05_add_norm(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(),
                                            _rows_2d(w, "linear weight"), _ptr(bias), stream.data_ptr(),
                                            _rows_2d(stream, "stream"), M, N, K, norm_weight.data_ptr(), float(eps),
                                            out.data_ptr(), N, scratch.data_ptr(), scratch.numel(),
-                                           status_word().data_ptr(), _stream())
+                                           status_word().data_ptr(), float(alpha), _stream())
         if _check(rc, lib) != UNSUPPORTED:
             return out
-    linear(x, w, bias, GEMM_ADD_F32, out=stream)
+    linear(x, w, bias, GEMM_ADD_F32, out=stream, alpha=alpha)
     return rmsnorm(stream, norm_weight, eps, out_dtype)
 
 
@@ -539,12 +609,15 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               q_start: torch.Tensor, start_pos: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
               num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
-              force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0) -> torch.Tensor:
+              force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0,
+              sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
     pages [num_pages, kv_heads, page_size, head_dim] already hold the keys and values of
-    every position up to each portion's last token.  Returns [T, heads*head_dim].
+    every position up to each portion's last token.  Returns [T, heads*value_dim].  The values may have
+    a size of their own: v pages [num_pages, kv_heads, page_size, value_dim].  ``sink`` (float32 [heads]):
+    a learned score per head that joins the softmax's denominator once, unscaled, with no key or value.
     ``split_tokens`` > 0 cuts the keys into runs of that many positions (a multiple of 64)
     that are attended in parallel and merged; 0 picks a value from the batch shape.
     ``decode_prefix``: how many sequences at the head of the batch are known to bring one token each
@@ -559,15 +632,23 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                     ("positions", positions), ("seq_of_token", seq_of_token)):
         _want(t, name, torch.int32)
     num_pages, page_kv, page_size, page_hd = k_pages.shape
-    if page_kv != kv_heads or page_hd != head_dim or v_pages.shape != k_pages.shape:
-        raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim}], got {tuple(k_pages.shape)}")
+    if (page_kv != kv_heads or page_hd != head_dim or v_pages.dim() != 4
+            or tuple(v_pages.shape[:3]) != tuple(k_pages.shape[:3])):
+        raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {head_dim}] and the like for the values, "
+                          f"got {tuple(k_pages.shape)} and {tuple(v_pages.shape)}")
+    value_dim = v_pages.shape[3]
+    if sink is not None:
+        _want(sink, "attention sinks", torch.float32)
+        if sink.numel() != heads:
+            raise KernelError(f"attention: {sink.numel()} sinks for {heads} heads")
     max_pages = block_table.shape[1]
     if out is None:
-        out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((tokens, heads * value_dim), dtype=q.dtype, device=q.device)
     _want(out, "attention output", q.dtype, contiguous=False)
     out_stride = _rows_2d(out, "attention output")
     use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt
-               and mma_attention_supports(head_dim, heads, kv_heads, page_size))
+               and mma_attention_supports(head_dim, heads, kv_heads, page_size)
+               and value_dim == head_dim and sink is None)
     if use_mma:
         lib = attention_lib(head_dim)
         prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 else 0
@@ -594,7 +675,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
                                   block_table.data_ptr(), max_pages, num_pages, page_size, positions.data_ptr(),
                                   seq_of_token.data_ptr(), out.data_ptr(), out_stride, tokens, heads, kv_heads,
-                                  head_dim, float(scale), window, int(q.dtype == torch.bfloat16),
+                                  head_dim, value_dim, _ptr(sink), float(scale), window, int(q.dtype == torch.bfloat16),
                                   status_word().data_ptr(), _stream()), lib)
     return out
 

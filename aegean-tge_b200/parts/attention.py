@@ -9,6 +9,14 @@ then the output projection added to the stream.  Here q, k and v are one
 product over row-concatenated weights with the bias in its epilogue, the
 rotation and the cache write are one kernel, and the output projection adds
 into the float32 stream in its epilogue.
+
+Options that other designs add, all off by default: values of a size of
+their own (``value_dim``); an RMS norm of q and of k before the scores,
+over each head or over a token's whole projection (``qk_norm``); a sink, one
+learned score per head that joins the softmax's denominator with no key or
+value behind it (``sinks``); and a blend of the values with those that an
+earlier layer computed for the same token (``value_mix``).  With a norm or a
+blend, one kernel normalises, blends and stores after the q/k/v product.
 """
 from __future__ import annotations
 
@@ -24,8 +32,12 @@ from .base import (MIXERS, POSITIONS, LayerCache, Mixer, PagedCacheSpec, ParamSp
 class GQAttention(Mixer):
     """params: ``hidden_size``, ``heads``, ``kv_heads``, ``head_dim``,
     ``qkv_bias`` (bool), ``o_bias`` (bool), ``window`` (None or tokens),
-    ``position`` (a PartSpec), optional ``scale``.
-    weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``.
+    ``position`` (a PartSpec), optional ``scale``; optional ``value_dim`` (default ``head_dim``),
+    ``qk_norm`` (None, or ``{"scope": "projection" | "head", "eps": e}``), ``sinks`` (bool),
+    ``value_mix`` (None, ``"first"``: this layer's values are kept for the step under ``value_mix_key``, or
+    ``"blend"``: v <- (1 - w) v + w v_first with the learned scalar w).
+    weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``; ``q_norm.weight`` / ``k_norm.weight``
+    (float32, the projection's or one head's size); ``sink`` [heads]; ``value_mix.weight`` (a scalar).
     """
     graph_safe = True
     can_defer_norm = True
@@ -46,11 +58,35 @@ class GQAttention(Mixer):
         if self.window is not None and int(self.window) <= 0:
             raise ValueError("attention: a window must be positive")
         self.scale = float(p.get("scale", self.head_dim ** -0.5))
+        self.value_dim = int(p.get("value_dim", self.head_dim))
+        norm = p.get("qk_norm")
+        self.qk_norm = None if norm is None else (str(norm["scope"]), float(norm["eps"]))
+        if self.qk_norm is not None and (self.qk_norm[0] not in ("projection", "head") or not self.qk_norm[1] > 0.0):
+            raise ValueError(f"attention: qk_norm {norm!r} needs scope 'projection' or 'head' and a positive eps")
+        self.sinks = bool(p.get("sinks", False))
+        self.value_mix = p.get("value_mix")
+        if self.value_mix not in (None, "first", "blend"):
+            raise ValueError(f"attention: value_mix {self.value_mix!r} is none of None, 'first', 'blend'")
+        self.value_mix_key = ("value_mix", str(p.get("value_mix_key", "values")))
+        if self.value_dim <= 0:
+            raise ValueError("attention: value_dim must be positive")
         position: PartSpec = p.get("position", PartSpec("none"))
         self.position = build_part(POSITIONS, position, env)
         self.graph_safe = bool(self.position.graph_safe)
         self.q_dim = self.heads * self.head_dim
         self.kv_dim = self.kv_heads * self.head_dim
+        self.v_dim = self.kv_heads * self.value_dim
+        self.o_dim = self.heads * self.value_dim
+        # the plain layer: rotation, store and attention as the fused kernels know them
+        self.plain = self.qk_norm is None and self.value_mix is None and self.value_dim == self.head_dim
+        tables = self.position.rotary_tables()
+        self.rotates = tables is None or tables[2] > 0
+        if self.value_dim != self.head_dim and self.rotates:
+            raise ValueError("attention: the rotate-and-store kernel needs values of the keys' size")
+        self.q_norm_w: Optional[torch.Tensor] = None
+        self.k_norm_w: Optional[torch.Tensor] = None
+        self.sink: Optional[torch.Tensor] = None
+        self.mix_w: Optional[torch.Tensor] = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
@@ -60,13 +96,22 @@ class GQAttention(Mixer):
         specs = {
             "q.weight": ParamSpec((self.q_dim, self.hidden)),
             "k.weight": ParamSpec((self.kv_dim, self.hidden)),
-            "v.weight": ParamSpec((self.kv_dim, self.hidden)),
-            "o.weight": ParamSpec((self.hidden, self.q_dim)),
+            "v.weight": ParamSpec((self.v_dim, self.hidden)),
+            "o.weight": ParamSpec((self.hidden, self.o_dim)),
         }
+        if self.qk_norm is not None:
+            per_head = self.qk_norm[0] == "head"
+            specs["q_norm.weight"] = ParamSpec((self.head_dim if per_head else self.q_dim,), role="vector")
+            specs["k_norm.weight"] = ParamSpec((self.head_dim if per_head else self.kv_dim,), role="vector")
+        if self.sinks:
+            specs["sink"] = ParamSpec((self.heads,), role="vector")
+        if self.value_mix is not None:
+            # the first layer of a chain has the scalar in its checkpoint too, and does not use it
+            specs["value_mix.weight"] = ParamSpec((), role="vector", optional=self.value_mix != "blend")
         if self.qkv_bias:
             specs["q.bias"] = ParamSpec((self.q_dim,), role="vector")
             specs["k.bias"] = ParamSpec((self.kv_dim,), role="vector")
-            specs["v.bias"] = ParamSpec((self.kv_dim,), role="vector")
+            specs["v.bias"] = ParamSpec((self.v_dim,), role="vector")
         if self.o_bias:
             specs["o.bias"] = ParamSpec((self.hidden,), role="vector")
         return specs
@@ -78,23 +123,59 @@ class GQAttention(Mixer):
             self.b_qkv = torch.cat([tensors["q.bias"], tensors["k.bias"], tensors["v.bias"]]).contiguous()
         self.w_o = tensors["o.weight"].contiguous()
         self.b_o = tensors["o.bias"].contiguous() if self.o_bias else None
+        if self.qk_norm is not None:
+            self.q_norm_w = tensors["q_norm.weight"].contiguous()
+            self.k_norm_w = tensors["k_norm.weight"].contiguous()
+        if self.sinks:
+            self.sink = tensors["sink"].contiguous()
+        if self.value_mix == "blend":
+            self.mix_w = tensors["value_mix.weight"].reshape(1).contiguous()
 
     def flops(self, tokens: int, pairs: float) -> float:
-        products = 2.0 * tokens * (self.q_dim + 2 * self.kv_dim + self.q_dim) * self.hidden
-        return products + 4.0 * self.heads * self.head_dim * pairs         # scores and weighted values
+        products = 2.0 * tokens * (self.q_dim + self.kv_dim + self.v_dim + self.o_dim) * self.hidden
+        return products + 2.0 * self.heads * (self.head_dim + self.value_dim) * pairs     # scores and weighted values
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
-        entry = (self.kv_heads, self.head_dim)
-        return PagedCacheSpec(entries=(("k", entry), ("v", entry)),
+        return PagedCacheSpec(entries=(("k", (self.kv_heads, self.head_dim)), ("v", (self.kv_heads, self.value_dim))),
                               window=None if self.window is None else int(self.window))
 
-    def attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
-        """Everything up to, not including, the output projection: [T, heads*head_dim]."""
+    def attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Everything up to, not including, the output projection: [T, heads*value_dim] (into ``out`` if given)."""
         ops = self.ops
         k_pages, v_pages = cache.paged["k"], cache.paged["v"]
         table = ctx.block_tables[cache.group]
         tables = self.position.rotary_tables()
-        if tables is not None and cache.owner:
+        if not self.plain:
+            qkv = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
+            other = blend = None
+            if self.value_mix == "blend":
+                if self.value_mix_key not in ctx.scratch:
+                    raise RuntimeError("attention: no earlier layer of this step left values to blend with")
+                other, blend = ctx.scratch[self.value_mix_key], self.mix_w
+            store_here = cache.owner and not self.rotates     # a rotated layer stores after its rotation
+            q_w, k_w, eps, per_head = self.q_norm_w, self.k_norm_w, 1.0, False
+            if self.qk_norm is not None:
+                per_head, eps = self.qk_norm[0] == "head", self.qk_norm[1]
+            ops.qk_norm_kv_store(qkv, q_w, k_w, eps, per_head, ctx.positions, ctx.seq_of_token,
+                                 table if store_here else None, k_pages if store_here else None,
+                                 v_pages if store_here else None, self.heads, self.kv_heads, self.head_dim,
+                                 self.value_dim, v_other=other, blend=blend)
+            if self.value_mix == "first":
+                ctx.scratch[self.value_mix_key] = qkv[:, self.q_dim + self.kv_dim:self.q_dim + self.kv_dim + self.v_dim]
+            if self.rotates:
+                if tables is None:
+                    q = qkv[:, :self.q_dim].view(-1, self.heads, self.head_dim)
+                    k = qkv[:, self.q_dim:self.q_dim + self.kv_dim].view(-1, self.kv_heads, self.head_dim)
+                    self.position.apply(q, k, ctx.positions)
+                    cos = sin = None
+                    rotary = 0
+                else:
+                    cos, sin, rotary = tables
+                ops.rope_kv_store(qkv, cos, sin, rotary, ctx.positions, ctx.seq_of_token, table,
+                                  k_pages if cache.owner else None, v_pages if cache.owner else None,
+                                  self.heads, self.kv_heads, self.head_dim)
+        elif tables is not None and cache.owner:
             # product, bias, rotation and cache store together (one or two kernels, chosen by batch size)
             cos, sin, rotary = tables
             qkv = ops.linear_qkv_rope_store(h, self.w_qkv, self.b_qkv, cos, sin, rotary, ctx.positions,
@@ -117,7 +198,13 @@ class GQAttention(Mixer):
                              ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads,
                              self.kv_heads, self.head_dim, self.scale, window=int(self.window or 0),
                              split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
-                             decode_prefix=ctx.decode_prefix)
+                             decode_prefix=ctx.decode_prefix, sink=self.sink, out=out)
+
+    def inner(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.attend(h, ctx, cache, out=out)
+
+    def output_projection(self):
+        return self.w_o, self.b_o
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_STORE)

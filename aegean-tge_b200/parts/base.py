@@ -210,6 +210,17 @@ class Mixer(Part):
         """h: run dtype [T, H] (already normed) -> [T, H] to be added to the stream."""
         raise NotImplementedError
 
+    def inner(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache,
+              out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """For mixers that end in a plain product: everything before it, [T, inner width], written into ``out``
+        (a view with dense rows) when one is given.  With :meth:`output_projection` it lets a block run that
+        last product itself, for instance together with the feed-forward's.  None: this mixer cannot."""
+        return None
+
+    def output_projection(self) -> Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]]:
+        """(weight [H, inner width], bias or None) of the last product, or None."""
+        return None
+
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache,
                     next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:
         """Adds the mixer's output to the float32 stream ``x`` in place.
@@ -228,6 +239,13 @@ class FeedForward(Part):
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
+    def inner(self, h: torch.Tensor, ctx: StepContext, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """As :meth:`Mixer.inner`: the activated inner rows [T, inner width], or None."""
+        return None
+
+    def output_projection(self) -> Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]]:
+        return None
+
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext,
                     next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:
         """As ``Mixer.forward_add``: adds into ``x``; may return ``next_norm(x)`` if it computed it."""
@@ -238,13 +256,19 @@ class FeedForward(Part):
 class Block:
     """Arrangement of one layer's parts around the residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, ffn_norm: Norm,
-                 env: BuildEnv):
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm, ffn_norm: Optional[Norm],
+                 env: BuildEnv, params: Optional[Dict[str, Any]] = None):
+        """``feed_forward`` and ``ffn_norm`` may be None for arrangements that do without; ``params`` are the
+        arrangement's own constants (``LayerSpec.block_params``)."""
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
         self.ffn_norm = ffn_norm
         self.env = env
+        self.params = dict(params or {})
+
+    def loaded(self) -> None:
+        """Called once all parts have their parameters: a block that fuses products across its parts repacks here."""
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache, h: Optional[torch.Tensor] = None,
                 next_norm: Optional[Norm] = None) -> Optional[torch.Tensor]:
@@ -260,8 +284,9 @@ class Block:
     passes_deferred_rows = False
 
     def parts(self) -> Dict[str, Part]:
-        return {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
-                "ffn_norm": self.ffn_norm, "feed_forward": self.feed_forward}
+        named = {"mixer_norm": self.mixer_norm, "mixer": self.mixer,
+                 "ffn_norm": self.ffn_norm, "feed_forward": self.feed_forward}
+        return {name: part for name, part in named.items() if part is not None}
 
 
 # ----------------------------------------------------------------------------

@@ -1,6 +1,8 @@
 """Arrangements of a mixer and a feed-forward around the residual stream."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 
 from .base import BLOCKS, Block, LayerCache, StepContext
@@ -27,3 +29,75 @@ class PreNormBlock(Block):
             h = self.ffn_norm.forward(x)
         defer = {"defer": True} if self.feed_forward.can_defer_norm and next_takes_deferred else {}
         return self.feed_forward.forward_add(h, x, ctx, next_norm=next_norm, **defer)
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(Block):
+    """h = norm(x); x += m * (mixer(h) + ffn(h)): one norm, both sublayers read its output.
+
+    params: ``residual_mult`` (m, default 1).  The feed-forward may be absent (x += m * mixer(h)).
+
+    When both sublayers end in a plain product (``inner`` / ``output_projection``), the two products are one:
+    the mixer's inner rows and the feed-forward's activated rows are written side by side into one buffer
+    [T, a | g] and multiplied by the column-concatenated weights [Wo | Wdown], so the stream is read and written
+    once, with m applied in that product's epilogue, and the sum of the two sublayers is formed in float32 inside
+    the accumulator.  For small batches the same kernel that adds the product into the stream also applies the
+    next layer's norm.  Sublayers that cannot hand out their last product are run whole and added one by one.
+    """
+
+    passes_deferred_rows = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, env, params=None):
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, env, params)
+        if ffn_norm is not None:
+            raise ValueError("parallel block: it has one norm; the feed-forward reads the mixer's")
+        self.mult = float(self.params.get("residual_mult", 1.0))
+        self.w_out: Optional[torch.Tensor] = None
+        self.b_out: Optional[torch.Tensor] = None
+        self.split = 0
+
+    def loaded(self) -> None:
+        """Concatenates the two output weights along their columns, once the parts have theirs."""
+        mixer_out = self.mixer.output_projection()
+        if mixer_out is None:
+            return
+        if self.feed_forward is None:
+            self.w_out, self.b_out = mixer_out
+            self.split = mixer_out[0].shape[1]
+            return
+        ffn_out = self.feed_forward.output_projection()
+        if ffn_out is None:
+            return
+        (w_a, b_a), (w_f, b_f) = mixer_out, ffn_out
+        self.split = w_a.shape[1]
+        self.w_out = torch.cat([w_a, w_f], dim=1).contiguous()
+        # the parts' own copies are not needed again: this block runs their last products
+        self.mixer.w_o = None
+        self.feed_forward.w_down = None
+        if b_a is not None or b_f is not None:
+            zero = torch.zeros(w_a.shape[0], dtype=torch.float32, device=w_a.device)
+            self.b_out = ((b_a if b_a is not None else zero) + (b_f if b_f is not None else zero)).contiguous()
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None, next_takes_deferred=False):
+        ops = self.env.ops
+        if h is None:
+            h = self.mixer_norm.forward(x)
+        if self.w_out is None:
+            # whole sublayers, added one by one
+            if isinstance(h, ops.DeferredRows):
+                h = h.complete()
+            ops.add_to_stream(x, self.mixer.forward(h, ctx, cache), alpha=self.mult)
+            if self.feed_forward is not None:
+                ops.add_to_stream(x, self.feed_forward.forward(h, ctx), alpha=self.mult)
+            return None
+        tokens = x.shape[0]
+        inner = torch.empty((tokens, self.w_out.shape[1]), dtype=self.env.dtype, device=x.device)
+        if self.feed_forward is not None:
+            self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
+        self.mixer.inner(h, ctx, cache, out=inner[:, :self.split])
+        fused = next_norm.fusable() if next_norm is not None else None
+        if fused is not None:
+            return ops.linear_add_norm(inner, self.w_out, self.b_out, x, fused[0], fused[1], self.env.dtype,
+                                       defer=bool(next_takes_deferred), alpha=self.mult)
+        ops.linear(inner, self.w_out, self.b_out, ops.GEMM_ADD_F32, out=x, alpha=self.mult)
+        return None

@@ -40,13 +40,19 @@ class TokenEmbedding(Part):
 
 @HEADS.register("linear_head")
 class LinearHead(Part):
-    """params: ``vocab_size``, ``hidden_size``.  weights: ``weight`` [vocab, hidden]."""
+    """params: ``vocab_size``, ``hidden_size``; optional ``logit_scale`` (multiplies the logits, in the product's
+    epilogue) and ``soft_cap`` (then logits <- cap * tanh(logits / cap), float32).  weights: ``weight`` [vocab, hidden]."""
     graph_safe = True
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.logit_scale = float(spec.params.get("logit_scale", 1.0))
+        cap = spec.params.get("soft_cap")
+        self.cap = None if cap is None else float(cap)
+        if self.cap is not None and not self.cap > 0.0:
+            raise ValueError("linear_head: soft_cap must be positive")
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -59,4 +65,5 @@ class LinearHead(Part):
         return 2.0 * tokens * self.vocab * self.hidden
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.ops.linear(h, self.weight, None, self.ops.GEMM_STORE_F32)
+        logits = self.ops.linear(h, self.weight, None, self.ops.GEMM_STORE_F32, alpha=self.logit_scale)
+        return logits if self.cap is None else self.ops.soft_cap(logits, self.cap)

@@ -57,3 +57,57 @@ class SwiGLU(FeedForward):
             return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype, defer=defer)
         self.ops.linear(a, self.w_down, None, self.ops.GEMM_ADD_F32, out=x)
         return None
+
+
+@FEED_FORWARDS.register("dense_mlp")
+class DenseMLP(FeedForward):
+    """The ungated feed-forward: d = Wdown act(Wup h), no biases.
+
+    params: ``hidden_size``, ``intermediate_size``, ``activation`` (``"gelu"``: 0.5 z (1 + erf(z / sqrt 2)), the
+    default, or ``"gelu_tanh"``: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  weights: ``up|down.weight``.
+    The activation is the epilogue of the up product.
+    """
+    graph_safe = True
+    can_defer_norm = True
+    takes_deferred_rows = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inner_size = int(spec.params["intermediate_size"])
+        activation = str(spec.params.get("activation", "gelu"))
+        if activation not in ("gelu", "gelu_tanh"):
+            raise ValueError(f"dense_mlp: unknown activation '{activation}'")
+        if self.hidden <= 0 or self.inner_size <= 0:
+            raise ValueError("dense_mlp: sizes must be positive")
+        self.epilogue = self.ops.GEMM_GELU if activation == "gelu" else self.ops.GEMM_GELU_TANH
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"up.weight": ParamSpec((self.inner_size, self.hidden)),
+                "down.weight": ParamSpec((self.hidden, self.inner_size))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up = tensors["up.weight"].contiguous()
+        self.w_down = tensors["down.weight"].contiguous()
+
+    def flops(self, tokens: int, pairs: float) -> float:
+        return 2.0 * tokens * 2 * self.inner_size * self.hidden
+
+    def inner(self, h, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.ops.linear(h, self.w_up, None, self.epilogue, out=out)
+
+    def output_projection(self):
+        return self.w_down, None
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        return self.ops.linear(self.inner(h, ctx), self.w_down, None, self.ops.GEMM_STORE)
+
+    def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None, defer: bool = False):
+        a = self.inner(h, ctx)
+        fused = next_norm.fusable() if next_norm is not None else None
+        if fused is not None:
+            return self.ops.linear_add_norm(a, self.w_down, None, x, fused[0], fused[1], self.env.dtype, defer=defer)
+        self.ops.linear(a, self.w_down, None, self.ops.GEMM_ADD_F32, out=x)
+        return None

@@ -41,9 +41,13 @@ def registered_architectures() -> Tuple[str, ...]:
 
 def architecture_of(raw_config: Dict[str, Any]) -> Architecture:
     names = raw_config.get("architectures")
-    if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise ConfigError("config.json: missing key 'architectures' (a list with the model class name)")
-    name = names[0]
+    if isinstance(names, list) and names and isinstance(names[0], str):
+        name = names[0]
+    elif isinstance(raw_config.get("architecture"), str):        # some designs name themselves with one string
+        name = raw_config["architecture"]
+    else:
+        raise ConfigError("config.json: missing key 'architectures' (a list with the model class name) "
+                          "or 'architecture' (the name)")
     if name not in _ARCHITECTURES:
         raise ConfigError(f"config.json: architecture '{name}' is not registered; "
                           f"registered: {', '.join(registered_architectures()) or '(none)'}")
