@@ -33,9 +33,18 @@ namespace {
 
 constexpr int HD = TGE_HEAD_DIM;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+// Values may have a size of their own (-DTGE_VALUE_DIM=...).  The kernels fed by cp.async take any pair of
+// sizes; those fed by TMA and the tcgen05 kernels are compiled for equal sizes only.
+#ifndef TGE_VALUE_DIM
+#define TGE_VALUE_DIM TGE_HEAD_DIM
+#endif
+constexpr int DV = TGE_VALUE_DIM;
+static_assert(DV % 16 == 0 && DV >= 16 && DV <= 256, "value size must be a multiple of 16 up to 256");
+#define TGE_TMA_KERNELS (TGE_HEAD_DIM % 64 == 0 && TGE_VALUE_DIM == TGE_HEAD_DIM)
 constexpr int BKV = 64;              // key positions per shared-memory tile
 constexpr int ROW_ELEMS = HD + 8;    // padded row: an odd count of 16-byte chunks keeps ldmatrix conflict-free
-constexpr int CHUNKS = HD / 8;       // 16-byte chunks per row
+constexpr int V_ROW_ELEMS = DV + 8;  // the same for a row of values
+constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
   const __nv_bfloat16* q;
@@ -44,6 +53,7 @@ struct AttnParams {
   const int* block_table;
   const int* q_start;
   const int* start_pos;
+  const float* sink;         // null, or one score per query head that joins the denominator once, unscaled
   __nv_bfloat16* out;
   float* partial_o;
   float* partial_ml;
@@ -58,6 +68,14 @@ struct AttnParams {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// The denominator `l` (relative to the running maximum `m_log2`, in base-2 units) with the head's sink in it.
+// exp2(sink - m) may overflow to +inf when every score lies far below the sink: the row's output is then 0,
+// which is its limit.
+__device__ __forceinline__ float with_sink(const AttnParams& p, int head, float m_log2, float l) {
+  if (p.sink == nullptr) return l;
+  return l + exp2f(p.sink[head] * LOG2E - (m_log2 == -INFINITY ? 0.0f : m_log2));
+}
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
@@ -86,20 +104,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // Copies positions [k0, k0 + BKV) of one kv head into a shared tile; positions
 // outside [lo, hi) are zero-filled so that masked columns never meet NaNs.
-template <int NWARPS>
+template <int NWARPS, int WIDTH = HD>
 __device__ __forceinline__ void load_tile(const AttnParams& p, const __nv_bfloat16* pages, const int* table, int kvh,
                                           __nv_bfloat16* tile, int k0, int lo, int hi, bool& bad_page) {
+  constexpr int CHUNKS = WIDTH / 8;      // 16-byte chunks per row
   for (int c = threadIdx.x; c < BKV * CHUNKS; c += NWARPS * 32) {
     const int j = c / CHUNKS, part = c - j * CHUNKS;
     const int kpos = k0 + j;
-    const uint32_t dst = smem_u32(tile + j * ROW_ELEMS + part * 8);
+    const uint32_t dst = smem_u32(tile + j * (WIDTH + 8) + part * 8);
     const void* src = pages;
     int bytes = 0;
     if (kpos >= lo && kpos < hi) {
       const int page_index = kpos >> p.page_shift;
       const int page = page_index < p.max_pages ? table[page_index] : -1;
       if (page >= 0 && page < p.num_pages) {
-        src = pages + ((((size_t)page * p.kv_heads + kvh) << p.page_shift) + (kpos & (p.page_size - 1))) * HD + part * 8;
+        src = pages + ((((size_t)page * p.kv_heads + kvh) << p.page_shift) + (kpos & (p.page_size - 1))) * WIDTH + part * 8;
         bytes = 16;
       } else {
         bad_page = true;
@@ -113,7 +132,7 @@ template <int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [2][BKV][ROW_ELEMS]
-  __nv_bfloat16* sV = sK + 2 * BKV * ROW_ELEMS;                             // [2][BKV][ROW_ELEMS]
+  __nv_bfloat16* sV = sK + 2 * BKV * ROW_ELEMS;                             // [2][BKV][V_ROW_ELEMS]
   __shared__ int tile_info[2];
   pdl_trigger();
   pdl_wait();
@@ -178,9 +197,9 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
   }
 
-  float o_acc[HD / 8][4];
+  float o_acc[DV / 8][4];
 #pragma unroll
-  for (int d = 0; d < HD / 8; ++d)
+  for (int d = 0; d < DV / 8; ++d)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -189,7 +208,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   const int k_first = lo / BKV * BKV;
   const int num_tiles = (hi - k_first + BKV - 1) / BKV;
   load_tile<NWARPS>(p, p.k_pages, table, kvh, sK, k_first, lo, hi, bad_page);
-  load_tile<NWARPS>(p, p.v_pages, table, kvh, sV, k_first, lo, hi, bad_page);
+  load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV, k_first, lo, hi, bad_page);
   cp_async_commit();
 
   for (int it = 0; it < num_tiles; ++it) {
@@ -197,7 +216,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int k0 = k_first + it * BKV;
     if (it + 1 < num_tiles) {
       load_tile<NWARPS>(p, p.k_pages, table, kvh, sK + (stage ^ 1) * BKV * ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
-      load_tile<NWARPS>(p, p.v_pages, table, kvh, sV + (stage ^ 1) * BKV * ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
+      load_tile<NWARPS, DV>(p, p.v_pages, table, kvh, sV + (stage ^ 1) * BKV * V_ROW_ELEMS, k0 + BKV, lo, hi, bad_page);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -205,7 +224,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
     __syncthreads();
     const __nv_bfloat16* tK = sK + stage * BKV * ROW_ELEMS;
-    const __nv_bfloat16* tV = sV + stage * BKV * ROW_ELEMS;
+    const __nv_bfloat16* tV = sV + stage * BKV * V_ROW_ELEMS;
 
     // S = Q K^T for 16 rows x 64 keys
     float s_acc[BKV / 8][4];
@@ -263,7 +282,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       m_run[i] = m_new[i];
     }
 #pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
+    for (int d = 0; d < DV / 8; ++d) {
       o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
       o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
     }
@@ -277,12 +296,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
       pf[2] = pack_bf16(s_acc[2 * kk + 1][0], s_acc[2 * kk + 1][1]);
       pf[3] = pack_bf16(s_acc[2 * kk + 1][2], s_acc[2 * kk + 1][3]);
 #pragma unroll
-      for (int dt = 0; dt < HD / 8; dt += 2) {
+      for (int dt = 0; dt < DV / 8; dt += 2) {
         const int mi = lane >> 3;
         const int key = kk * 16 + (mi & 1) * 8 + (lane & 7);
         const int d = (dt + (mi >> 1)) * 8;
         uint32_t r0, r1, r2, r3;
-        ldmatrix_x4_trans(smem_u32(tV + key * ROW_ELEMS + d), r0, r1, r2, r3);
+        ldmatrix_x4_trans(smem_u32(tV + key * V_ROW_ELEMS + d), r0, r1, r2, r3);
         mma_bf16(o_acc[dt], pf, r0, r1);
         mma_bf16(o_acc[dt + 1], pf, r2, r3);
       }
@@ -301,18 +320,19 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
   for (int i = 0; i < 2; ++i) {
     if (!row_valid[i]) continue;
     if (p.num_splits == 1) {
-      const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
-      __nv_bfloat16* dst = p.out + (size_t)row_token[i] * p.out_stride + (size_t)row_head[i] * HD;
+      const float l_all = with_sink(p, row_head[i], m_run[i], l_run[i]);
+      const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+      __nv_bfloat16* dst = p.out + (size_t)row_token[i] * p.out_stride + (size_t)row_head[i] * DV;
 #pragma unroll
-      for (int d = 0; d < HD / 8; ++d) {
+      for (int d = 0; d < DV / 8; ++d) {
         *reinterpret_cast<uint32_t*>(dst + d * 8 + 2 * t4) =
             pack_bf16(o_acc[d][2 * i] * inv, o_acc[d][2 * i + 1] * inv);
       }
     } else {
       const size_t slot = ((size_t)split * p.total_tokens + row_token[i]) * p.heads + row_head[i];
-      float* dst = p.partial_o + slot * HD;
+      float* dst = p.partial_o + slot * DV;
 #pragma unroll
-      for (int d = 0; d < HD / 8; ++d) {
+      for (int d = 0; d < DV / 8; ++d) {
         *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
       }
       if (t4 == 0) {
@@ -332,7 +352,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
 // ---------------------------------------------------------------------------
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_STAGES = 3;
-constexpr int STAGE_ELEMS = 2 * BKV * ROW_ELEMS;   // K tile then V tile
+constexpr int STAGE_ELEMS = BKV * (ROW_ELEMS + V_ROW_ELEMS);   // K tile then V tile
 
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const AttnParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -375,9 +395,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
       qf[kc][i + 2] = valid ? *reinterpret_cast<const uint32_t*>(src + 8) : 0u;
     }
   }
-  float o_acc[HD / 8][4];
+  float o_acc[DV / 8][4];
 #pragma unroll
-  for (int d = 0; d < HD / 8; ++d)
+  for (int d = 0; d < DV / 8; ++d)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o_acc[d][e] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -389,7 +409,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < num_tiles) {
       load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, stages + s * STAGE_ELEMS, k_first + s * BKV, lo, hi, bad_page);
-      load_tile<DEC_WARPS>(p, p.v_pages, table, kvh, stages + s * STAGE_ELEMS + BKV * ROW_ELEMS, k_first + s * BKV, lo, hi, bad_page);
+      load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, stages + s * STAGE_ELEMS + BKV * ROW_ELEMS, k_first + s * BKV, lo, hi, bad_page);
     }
     cp_async_commit();
   }
@@ -401,7 +421,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
       if (next < num_tiles) {
         __nv_bfloat16* dst = stages + (next % DEC_STAGES) * STAGE_ELEMS;
         load_tile<DEC_WARPS>(p, p.k_pages, table, kvh, dst, k_first + next * BKV, lo, hi, bad_page);
-        load_tile<DEC_WARPS>(p, p.v_pages, table, kvh, dst + BKV * ROW_ELEMS, k_first + next * BKV, lo, hi, bad_page);
+        load_tile<DEC_WARPS, DV>(p, p.v_pages, table, kvh, dst + BKV * ROW_ELEMS, k_first + next * BKV, lo, hi, bad_page);
       }
       cp_async_commit();
     }
@@ -460,7 +480,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
       m_run[i] = m_new;
     }
 #pragma unroll
-    for (int d = 0; d < HD / 8; ++d) {
+    for (int d = 0; d < DV / 8; ++d) {
       o_acc[d][0] *= corr[0]; o_acc[d][1] *= corr[0];
       o_acc[d][2] *= corr[1]; o_acc[d][3] *= corr[1];
     }
@@ -470,12 +490,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     pf[2] = pack_bf16(s_acc[1][0], s_acc[1][1]);
     pf[3] = pack_bf16(s_acc[1][2], s_acc[1][3]);
 #pragma unroll
-    for (int dt = 0; dt < HD / 8; dt += 2) {
+    for (int dt = 0; dt < DV / 8; dt += 2) {
       const int mi = lane >> 3;
       const int key = warp * 16 + (mi & 1) * 8 + (lane & 7);
       const int d = (dt + (mi >> 1)) * 8;
       uint32_t r0, r1, r2, r3;
-      ldmatrix_x4_trans(smem_u32(tV + key * ROW_ELEMS + d), r0, r1, r2, r3);
+      ldmatrix_x4_trans(smem_u32(tV + key * V_ROW_ELEMS + d), r0, r1, r2, r3);
       mma_bf16(o_acc[dt], pf, r0, r1);
       mma_bf16(o_acc[dt + 1], pf, r2, r3);
     }
@@ -484,16 +504,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
   __syncthreads();                                      // every warp is done with the stages: reuse them
   if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
 
-  float* merge_o = reinterpret_cast<float*>(smem_raw);                  // [warps][16][HD]
-  float* merge_ml = merge_o + DEC_WARPS * 16 * HD;                      // [warps][16][2]
+  float* merge_o = reinterpret_cast<float*>(smem_raw);                  // [warps][16][DV]
+  float* merge_ml = merge_o + DEC_WARPS * 16 * DV;                      // [warps][16][2]
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     const int r = g8 + 8 * i;
-    float* dst = merge_o + ((size_t)warp * 16 + r) * HD;
+    float* dst = merge_o + ((size_t)warp * 16 + r) * DV;
 #pragma unroll
-    for (int d = 0; d < HD / 8; ++d)
+    for (int d = 0; d < DV / 8; ++d)
       *reinterpret_cast<float2*>(dst + d * 8 + 2 * t4) = make_float2(o_acc[d][2 * i], o_acc[d][2 * i + 1]);
     if (t4 == 0) {
       merge_ml[(warp * 16 + r) * 2] = m_run[i];
@@ -501,8 +521,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < p.group * HD; idx += DEC_WARPS * 32) {
-    const int r = idx / HD, d = idx - r * HD;
+  for (int idx = tid; idx < p.group * DV; idx += DEC_WARPS * 32) {
+    const int r = idx / DV, d = idx - r * DV;
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, merge_ml[(w * 16 + r) * 2]);
@@ -512,14 +532,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
     for (int w = 0; w < DEC_WARPS; ++w) {
       const float scale = exp2f(merge_ml[(w * 16 + r) * 2] - m_use);
       l += scale * merge_ml[(w * 16 + r) * 2 + 1];
-      acc += scale * merge_o[((size_t)w * 16 + r) * HD + d];
+      acc += scale * merge_o[((size_t)w * 16 + r) * DV + d];
     }
     const int head = kvh * p.group + r;
     if (p.num_splits == 1) {
-      p.out[(size_t)token * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+      const float l_all = with_sink(p, head, m, l);
+      p.out[(size_t)token * p.out_stride + (size_t)head * DV + d] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
     } else {
       const size_t slot = ((size_t)split * p.total_tokens + token) * p.heads + head;
-      p.partial_o[slot * HD + d] = acc;
+      p.partial_o[slot * DV + d] = acc;
       if (d == 0) {
         p.partial_ml[slot * 2] = m;
         p.partial_ml[slot * 2 + 1] = l;
@@ -537,7 +558,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_decode_kernel(const 
 // Stages are cleared once at the start: boxes of pages a request does not own are never fetched,
 // and what masked columns multiply must be finite.
 // ---------------------------------------------------------------------------
-#if TGE_HEAD_DIM % 64 == 0
+#if TGE_TMA_KERNELS
 constexpr int TMA_BLOCKS = HD / 64;                       // 64-column blocks per row
 constexpr int TMA_TILE_BYTES = BKV * HD * 2;              // one K (or V) tile
 constexpr int TMA_STAGE_BYTES = 2 * TMA_TILE_BYTES;
@@ -831,7 +852,8 @@ __global__ void __launch_bounds__((4 * GROUPS + 1) * 32) attention_decode_tma_ke
     }
     const int head = kvh * p.group + r;
     if (p.num_splits == 1) {
-      p.out[(size_t)token * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+      const float l_all = with_sink(p, head, m, l);
+      p.out[(size_t)token * p.out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(l_all > 0.0f ? acc / l_all : 0.0f);
     } else {
       const size_t slot = ((size_t)split * p.total_tokens + token) * p.heads + head;
       p.partial_o[slot * HD + d] = acc;
@@ -1102,7 +1124,8 @@ __global__ void __launch_bounds__(PRE_THREADS) attention_prefill_tma_kernel(
   for (int i = 0; i < 2; ++i) {
     if (!row_valid[i]) continue;
     if (p.num_splits == 1) {
-      const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+      const float l_all = with_sink(p, row_head[i], m_run[i], l_run[i]);
+      const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
       __nv_bfloat16* dst = p.out + (size_t)row_token[i] * p.out_stride + (size_t)row_head[i] * HD;
 #pragma unroll
       for (int d = 0; d < HD / 8; ++d)
@@ -1162,7 +1185,7 @@ const CUtensorMap* pool_map(const void* pages, int num_pages, int kv_heads, int 
   }
   return &maps.emplace(key, map).first->second;
 }
-#endif  // TGE_HEAD_DIM % 64 == 0
+#endif  // TGE_TMA_KERNELS
 
 // Merges the split states of one (token, head): out = sum_s 2^(m_s - M) acc_s / sum_s 2^(m_s - M) l_s,
 // over the splits that hold keys visible to the row, in split order.
@@ -1170,10 +1193,11 @@ template <int HELD>                                                  // splits w
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
-                                       int num_splits, int first_token) {
+                                       int num_splits, int first_token, const float* __restrict__ sink) {
   pdl_trigger();
   const int t = blockIdx.x + first_token, h = blockIdx.y;
   const int pos = positions[t];                                     // given to the step: not the previous kernel's work
+  const float sink_log2 = sink != nullptr ? sink[h] * LOG2E : -INFINITY;   // the sink joins the merged denominator once
   pdl_wait();
   const size_t stride = (size_t)total_tokens * heads;               // slots per split
   const size_t slot0 = (size_t)t * heads + h;
@@ -1189,10 +1213,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
     const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
     const int s_lo = first_key / split_tokens;
     const int s_hi = min(pos / split_tokens, num_splits - 1);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
       float o[HELD];
 #pragma unroll
-      for (int i = 0; i < HELD; ++i) o[i] = i < num_splits ? partial_o[((size_t)i * stride + slot0) * HD + d] : 0.0f;
+      for (int i = 0; i < HELD; ++i) o[i] = i < num_splits ? partial_o[((size_t)i * stride + slot0) * DV + d] : 0.0f;
 #pragma unroll
       for (int i = 0; i < HELD; ++i) {
         const bool live = i >= s_lo && i <= s_hi;
@@ -1210,7 +1234,8 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
         l += scale * ml[i].y;
         acc += scale * o[i];
       }
-      out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * (l > 0.0f ? 1.0f / l : 0.0f));
+      if (sink != nullptr) l += exp2f(sink_log2 - m_use);
+      out[(size_t)t * out_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * (l > 0.0f ? 1.0f / l : 0.0f));
     }
     return;
   }
@@ -1225,14 +1250,15 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
     const size_t slot = (size_t)s * stride + slot0;
     l += exp2f(partial_ml[slot * 2] - m_use) * partial_ml[slot * 2 + 1];
   }
+  if (sink != nullptr) l += exp2f(sink_log2 - m_use);
   const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
     float acc = 0.0f;
     for (int s = s_lo; s <= s_hi; ++s) {
       const size_t slot = (size_t)s * stride + slot0;
-      acc += exp2f(partial_ml[slot * 2] - m_use) * partial_o[slot * HD + d];
+      acc += exp2f(partial_ml[slot * 2] - m_use) * partial_o[slot * DV + d];
     }
-    out[(size_t)t * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(acc * inv);
+    out[(size_t)t * out_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -1240,19 +1266,19 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
 // instance, and beyond that the kernel walks the splits in a loop.
 void launch_merge(dim3 grid, cudaStream_t stream, const float* partial_o, const float* partial_ml, const int* positions,
                   __nv_bfloat16* out, int out_stride, int total_tokens, int heads, int window, int split_tokens,
-                  int num_splits, int first_token) {
-  const int threads = HD >= 128 ? 128 : (HD >= 64 ? 64 : 32);
+                  int num_splits, int first_token, const float* sink) {
+  const int threads = DV >= 128 ? 128 : (DV >= 64 ? 64 : 32);
   if (num_splits <= 16)
     tge_launch(attention_merge_kernel<16>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
-               total_tokens, heads, window, split_tokens, num_splits, first_token);
+               total_tokens, heads, window, split_tokens, num_splits, first_token, sink);
   else
     tge_launch(attention_merge_kernel<48>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
-               total_tokens, heads, window, split_tokens, num_splits, first_token);
+               total_tokens, heads, window, split_tokens, num_splits, first_token, sink);
 }
 
 template <int NWARPS>
 int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
-  const size_t smem = (size_t)4 * BKV * ROW_ELEMS * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)2 * BKV * (ROW_ELEMS + V_ROW_ELEMS) * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<NWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -1270,10 +1296,11 @@ int launch(const AttnParams& p, int tiles, cudaStream_t stream) {
 }  // namespace
 
 TGE_API int tge_attention_mma_head_dim() { return HD; }
+TGE_API int tge_attention_mma_value_dim() { return DV; }
 
-// Rows of scratch a call needs: float32 [splits, tokens, heads, HD] for acc and [splits, tokens, heads, 2] for (m, l).
+// Rows of scratch a call needs: float32 [splits, tokens, heads, DV] for acc and [splits, tokens, heads, 2] for (m, l).
 TGE_API long long tge_attention_mma_scratch_floats(int tokens, int heads, int num_splits) {
-  return num_splits > 1 ? (long long)num_splits * tokens * heads * (HD + 2) : 0;
+  return num_splits > 1 ? (long long)num_splits * tokens * heads * (DV + 2) : 0;
 }
 
 // q: [tokens, heads*HD] with row stride q_stride (elements); pages: [num_pages, kv_heads, page_size, HD].
@@ -1287,7 +1314,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int first_token, cudaStream_t stream) {
+                              int first_token, const float* sink, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
   TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
@@ -1303,7 +1330,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
   p.block_table = block_table; p.q_start = q_start; p.start_pos = start_pos;
-  p.out = (__nv_bfloat16*)out; p.status = status;
+  p.out = (__nv_bfloat16*)out; p.status = status; p.sink = sink;
   p.q_stride = q_stride; p.out_stride = out_stride;
   p.max_pages = max_pages; p.num_pages = num_pages; p.page_size = page_size;
   p.page_shift = 0;
@@ -1320,9 +1347,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.num_splits = num_splits;
   TGE_REQUIRE(num_splits == 1 || scratch != nullptr, "attention_mma: %d splits need scratch memory", num_splits);
   p.partial_o = scratch;
-  p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * HD : nullptr;
+  p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * DV : nullptr;
 
-#if TGE_HEAD_DIM % 64 == 0
+#if TGE_TMA_KERNELS
   if (max_q_len <= 1 && tokens == num_seqs && group <= 16 && page_size >= 8) {
     const CUtensorMap* map_k = pool_map(k_pages, num_pages, kv_heads, page_size);
     const CUtensorMap* map_v = pool_map(v_pages, num_pages, kv_heads, page_size);
@@ -1360,7 +1387,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens - first_token, heads);
-      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1387,12 +1414,12 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     if (rc != 0) return rc;
     if (num_splits > 1) {
       dim3 mgrid(tokens - first_token, heads);
-      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
       return tge_launched("attention_merge", 2);
     }
     return 1;
   }
-#if TGE_HEAD_DIM % 64 == 0
+#if TGE_TMA_KERNELS
   if (max_q_len > 1 && group <= 64 && page_size >= 8) {
     const CUtensorMap* map_k = pool_map(k_pages, num_pages, kv_heads, page_size);
     const CUtensorMap* map_v = pool_map(v_pages, num_pages, kv_heads, page_size);
@@ -1423,7 +1450,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
         if (rc2 != 0) return rc2;
         if (num_splits > 1) {
           dim3 mgrid(tokens - first_token, heads);
-          launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+          launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
           return tge_launched("attention_merge", 2);
         }
         return 1;
@@ -1445,7 +1472,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       if (rc != 0) return rc;
       if (num_splits > 1) {
         dim3 mgrid(tokens - first_token, heads);
-        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1468,7 +1495,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       if (rc != 0) return rc;
       if (num_splits > 1) {
         dim3 mgrid(tokens - first_token, heads);
-        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1488,7 +1515,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   if (rc != 0) return rc;
   if (num_splits > 1) {
     dim3 grid(tokens - first_token, heads);
-    launch_merge(grid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token);
+    launch_merge(grid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
     return tge_launched("attention_merge", 2);
   }
   return 1;
@@ -1504,7 +1531,7 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int decode_prefix, int prefix_split_tokens, cudaStream_t stream) {
+                              int decode_prefix, int prefix_split_tokens, const float* sink, cudaStream_t stream) {
   TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
               decode_prefix, num_seqs);
   TGE_REQUIRE(prefix_split_tokens >= 0 && prefix_split_tokens % BKV == 0,
@@ -1512,14 +1539,14 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
     return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
                               positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
-                              window, split_tokens, scratch, status, 0, stream);
+                              window, split_tokens, scratch, status, 0, sink, stream);
   const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
                                        start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
-                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, stream);
+                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, stream);
   if (first < 0) return first;
   const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
                                       num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,
                                       num_seqs - decode_prefix, tokens, max_q_len, max_ctx_len, out, out_stride, heads,
-                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, stream);
+                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, stream);
   return rest < 0 ? rest : first + rest;
 }

@@ -388,7 +388,9 @@ __global__ void __launch_bounds__(THREADS, 2) attention_prefill_tc_kernel(
     if (bad_page && p.status) atomicOr(p.status, TGE_STATUS_BAD_PAGE);
     mbar_wait_bounded(o_bar, (uint32_t)(num_tiles - 1) & 1u, p.status);
     fence_after();
-    const float inv = (p.num_splits == 1) ? (l_run > 0.0f ? 1.0f / l_run : 0.0f) : 1.0f;
+    // the running maximum is kept in the scores' own units here; the sink joins in scaled base-2 units
+    const float l_all = p.num_splits == 1 ? with_sink(p, row_head, m_run == -INFINITY ? -INFINITY : m_run * p.scale_log2, l_run) : l_run;
+    const float inv = (p.num_splits == 1) ? (l_all > 0.0f ? 1.0f / l_all : 0.0f) : 1.0f;
     const size_t slot = ((size_t)split * p.total_tokens + row_token) * p.heads + row_head;
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {

@@ -5,8 +5,9 @@ Three kinds of library exist:
 * ``libtge_runtime.so`` - the host runtime (page pools, cache bookkeeping,
   scheduler, step packing): plain C++, needs no CUDA;
 * ``libtge_core.so`` - every kernel that does not depend on the model;
-* ``libtge_attn_hd<N>.so`` - the tensor-core attention kernels for one head
-  size, compiled when a model with that head size is first built.
+* ``libtge_attn_hd<N>.so`` (``libtge_attn_hd<N>_vd<M>.so`` when values have a
+  size of their own) - the tensor-core attention kernels for one head size,
+  compiled when a model with that head size is first built.
 
 A library is rebuilt when the hash of its sources and flags changes.  Builds
 print a line per file so that a first call on a fresh checkout shows progress.
@@ -193,12 +194,18 @@ def build_core() -> str:
     return _build("libtge_core.so", CORE_SOURCES, [])
 
 
-def build_attention(head_dim: int) -> str:
-    if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
-        raise BuildError(f"the tensor-core attention kernel takes head sizes that are multiples of 16 "
-                         f"up to 256, not {head_dim}")
-    return _build(f"libtge_attn_hd{head_dim}.so", ["host_util.cu", "attention_mma.cu"],
-                  [f"-DTGE_HEAD_DIM={head_dim}"])
+def build_attention(head_dim: int, value_dim: int = 0) -> str:
+    """The attention library for keys of ``head_dim`` and values of ``value_dim`` (0: the same size)."""
+    value_dim = value_dim or head_dim
+    for size in (head_dim, value_dim):
+        if size % 16 != 0 or not 16 <= size <= 256:
+            raise BuildError(f"the tensor-core attention kernel takes head sizes that are multiples of 16 "
+                             f"up to 256, not {size}")
+    if value_dim == head_dim:
+        return _build(f"libtge_attn_hd{head_dim}.so", ["host_util.cu", "attention_mma.cu"],
+                      [f"-DTGE_HEAD_DIM={head_dim}"])
+    return _build(f"libtge_attn_hd{head_dim}_vd{value_dim}.so", ["host_util.cu", "attention_mma.cu"],
+                  [f"-DTGE_HEAD_DIM={head_dim}", f"-DTGE_VALUE_DIM={value_dim}"])
 
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:

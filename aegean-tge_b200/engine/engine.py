@@ -262,7 +262,7 @@ class Engine:
     def describe(self) -> Dict[str, Any]:
         kinds: Dict[str, int] = {}
         for layer in self.spec.layers:
-            name = f"{layer.mixer.kind}+{layer.feed_forward.kind}"
+            name = layer.mixer.kind + ("" if layer.feed_forward is None else f"+{layer.feed_forward.kind}")
             kinds[name] = kinds.get(name, 0) + 1
         return {
             "layer_kinds": ", ".join(f"{count} x {name}" for name, count in kinds.items()),

@@ -32,12 +32,12 @@ def build_spec(config: LepizenConfig) -> ModelSpec:
         m = layer.mixer
         weights = {"q.weight": prefix + "mix.q", "k.weight": prefix + "mix.k", "v.weight": prefix + "mix.v",
                    "o.weight": prefix + "mix.o", "q_norm.weight": prefix + "mix.q.norm",
-                   "k_norm.weight": prefix + "mix.k.norm", "sink": prefix + "mix.sink"}
+                   "k_norm.weight": prefix + "mix.k.norm", "sink": prefix + "mix.sink",
+                   "value_mix.weight": prefix + "mix.vmix"}        # used by blending layers, optional in the others
         value_mix = None
         if m.v_mix:
             value_mix = "blend" if seen_mixing else "first"
             seen_mixing = True
-            weights["value_mix.weight"] = prefix + "mix.vmix"
         mixer = PartSpec(
             "gqa_attention",
             {"hidden_size": width, "heads": m.heads, "kv_heads": m.kv_heads, "head_dim": m.dim, "value_dim": m.vdim,

@@ -36,7 +36,7 @@ class DeviceStatusError(RuntimeError):
 # libraries
 # ----------------------------------------------------------------------------
 _core_lib: Optional[ctypes.CDLL] = None
-_attn_libs: Dict[int, ctypes.CDLL] = {}
+_attn_libs: Dict[Tuple[int, int], ctypes.CDLL] = {}
 
 # Set to False to send bfloat16 products through the CUDA-core kernel (for A/B checks).
 USE_TCGEN05 = os.environ.get("TGE_NO_TCGEN05", "") == ""
@@ -107,25 +107,28 @@ def core() -> ctypes.CDLL:
     return _core_lib
 
 
-def attention_lib(head_dim: int) -> ctypes.CDLL:
-    if head_dim not in _attn_libs:
-        path = _build.build_attention(head_dim)
+def attention_lib(head_dim: int, value_dim: int = 0) -> ctypes.CDLL:
+    value_dim = value_dim or head_dim
+    if (head_dim, value_dim) not in _attn_libs:
+        path = _build.build_attention(head_dim, value_dim)
         lib = ctypes.CDLL(path)
         lib.tge_last_error.restype = ctypes.c_char_p
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
-                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr])
+                                            _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
+                                            _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
-        if lib.tge_attention_mma_head_dim() != head_dim:
+        if lib.tge_attention_mma_head_dim() != head_dim or lib.tge_attention_mma_value_dim() != value_dim:
             raise KernelError(f"{path} was built for another head size")
-        _attn_libs[head_dim] = lib
-    return _attn_libs[head_dim]
+        _attn_libs[(head_dim, value_dim)] = lib
+    return _attn_libs[(head_dim, value_dim)]
 
 
-def mma_attention_supports(head_dim: int, heads: int, kv_heads: int, page_size: int) -> bool:
-    return (head_dim % 16 == 0 and 16 <= head_dim <= 256 and heads % kv_heads == 0
-            and heads // kv_heads <= 64 and 64 % page_size == 0)
+def mma_attention_supports(head_dim: int, heads: int, kv_heads: int, page_size: int, value_dim: int = 0) -> bool:
+    value_dim = value_dim or head_dim
+    return (head_dim % 16 == 0 and 16 <= head_dim <= 256 and value_dim % 16 == 0 and 16 <= value_dim <= 256
+            and heads % kv_heads == 0 and heads // kv_heads <= 64 and 64 % page_size == 0)
 
 
 def loaded_libraries() -> Tuple[str, ...]:
@@ -647,10 +650,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     _want(out, "attention output", q.dtype, contiguous=False)
     out_stride = _rows_2d(out, "attention output")
     use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt
-               and mma_attention_supports(head_dim, heads, kv_heads, page_size)
-               and value_dim == head_dim and sink is None)
+               and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim))
     if use_mma:
-        lib = attention_lib(head_dim)
+        lib = attention_lib(head_dim, value_dim)
         prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 else 0
         prefix_split = split_tokens
         if split_tokens == 0:
@@ -669,7 +671,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
                                      split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
-                                     _stream()), lib)
+                                     _ptr(sink), _stream()), lib)
         return out
     lib = core()
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),

@@ -105,8 +105,9 @@ class GQAttention(Mixer):
             specs["k_norm.weight"] = ParamSpec((self.head_dim if per_head else self.kv_dim,), role="vector")
         if self.sinks:
             specs["sink"] = ParamSpec((self.heads,), role="vector")
-        if self.value_mix is not None:
-            # the first layer of a chain has the scalar in its checkpoint too, and does not use it
+        if self.value_mix is not None or "value_mix.weight" in self.spec.weights:
+            # only a blending layer uses the scalar; a checkpoint may hold one for the other layers too (the first
+            # of a chain, layers that do not mix), so a model spec may name it for them and it is then optional
             specs["value_mix.weight"] = ParamSpec((), role="vector", optional=self.value_mix != "blend")
         if self.qkv_bias:
             specs["q.bias"] = ParamSpec((self.q_dim,), role="vector")

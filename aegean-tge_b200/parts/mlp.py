@@ -80,7 +80,7 @@ class DenseMLP(FeedForward):
             raise ValueError(f"dense_mlp: unknown activation '{activation}'")
         if self.hidden <= 0 or self.inner_size <= 0:
             raise ValueError("dense_mlp: sizes must be positive")
-        self.epilogue = self.ops.GEMM_GELU if activation == "gelu" else self.ops.GEMM_GELU_TANH
+        self.activation = activation
         self.w_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -96,7 +96,8 @@ class DenseMLP(FeedForward):
         return 2.0 * tokens * 2 * self.inner_size * self.hidden
 
     def inner(self, h, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return self.ops.linear(h, self.w_up, None, self.epilogue, out=out)
+        epilogue = self.ops.GEMM_GELU if self.activation == "gelu" else self.ops.GEMM_GELU_TANH
+        return self.ops.linear(h, self.w_up, None, epilogue, out=out)
 
     def output_projection(self):
         return self.w_down, None
