@@ -202,3 +202,64 @@ def step_timeline(engine, batch: int, prompt_len: int, prefill: bool, portion: i
     rows.sort(key=lambda r: -r["us"])
     rows.append({"kernel": "span of the step under the profiler", "launches": len(events), "us": span, "share": 1.0})
     return rows
+
+
+# ----------------------------------------------------------------------------
+# two designs side by side at equal size
+# ----------------------------------------------------------------------------
+def paired_configs(width: int, heads: int, kv_heads: int, head_dim: int, gated_inner: int, layers: int,
+                   vocab: int) -> Dict[str, dict]:
+    """A Qwen2 and a Lepizen config.json of the same width, heads, layers, vocabulary and parameter count: the
+    ungated feed-forward gets one and a half times the gated one's inner width (two matrices instead of three)."""
+    qwen2 = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": layers,
+             "hidden_size": width, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim,
+             "intermediate_size": gated_inner, "vocab_size": vocab, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+             "tie_word_embeddings": False, "max_position_embeddings": 32768, "use_sliding_window": False,
+             "hidden_act": "silu"}
+    layer = {"type": "attention",
+             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                       "v_mix": True},
+             "mlp": {"kind": "dense", "ff": gated_inner * 3 // 2}}
+    lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
+               "logit_scale": 2.0, "logit_softcap": 30.0, "layers": [layer] * layers}
+    return {"qwen2": qwen2, "lepizen": lepizen}
+
+
+def compare_designs(configs: Dict[str, dict], prompt_len: int = 2048, batches=(8, 64), steps: int = 32, warmup: int = 3,
+                    page_size: int = 64, timelines: bool = True) -> Dict[str, dict]:
+    """Prefill and decode of each config (random weights drawn on the device, bfloat16), one engine at a time:
+    a ``prompt_len``-token prompt against the bf16 peak, decode steps of each batch after prompts of that length
+    against the copy bandwidth, and where the time of a prefill step and of a decode step of the first batch goes,
+    kernel by kernel."""
+    import gc
+    import time
+    from .engine.engine import Engine
+    out: Dict[str, dict] = {}
+    for name, config in configs.items():
+        gc.collect()
+        torch.cuda.empty_cache()
+        most = max(batches)
+        engine = Engine(random_config=config, seed=0, dtype="bfloat16", context=2 * prompt_len, page_size=page_size,
+                        max_tokens=most * (prompt_len + steps + warmup + 80) + prompt_len, max_batch_tokens=prompt_len,
+                        max_requests=most + 1)
+        row: Dict[str, object] = {"weight_gb": round(engine.model.weight_bytes() / 1e9, 3),
+                                  "step_param_gb": round(engine.model.step_param_bytes() / 1e9, 3)}
+        run = bench_prefill(engine, prompt_len, repeat=3, warmup=2, sustain_seconds=0.5)
+        row["prefill"] = {"tokens": prompt_len, "ms": round(run["burst_ms"], 3), "tok_s": round(prompt_len / (run["burst_ms"] * 1e-3), 1),
+                          "tflops": round(run["flops"] / (run["burst_ms"] * 1e-3) / 1e12, 1), "frac": round(run["burst_frac"], 4),
+                          "sustained_ms": round(run["sustained_ms"], 3), "sustained_frac": round(run["sustained_frac"], 4)}
+        for batch in batches:
+            torch.cuda.synchronize()
+            time.sleep(2.0)
+            run = bench_decode(engine, batch, prompt_len, steps=steps, warmup=warmup)
+            row[f"decode_b{batch}"] = {"ms_per_step": round(run["ms_per_step"], 4), "tok_s": round(run["tok_s"], 1),
+                                      "gbs": round(run["gbs"], 1), "hbm_frac": round(run["frac"], 4),
+                                      "launches_per_step": run["launches"] // run["steps"]}
+        if timelines:
+            keep = lambda rows: [{"kernel": r["kernel"], "launches": r["launches"], "us": round(r["us"], 1),
+                                  "share": round(r["share"], 4)} for r in rows[:12] + rows[-1:]]
+            row["prefill_kernels"] = keep(step_timeline(engine, 1, prompt_len, prefill=True))
+            row["decode_kernels"] = keep(step_timeline(engine, batches[0], prompt_len, prefill=False))
+        out[name] = row
+        del engine
+    return out

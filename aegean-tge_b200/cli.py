@@ -138,11 +138,14 @@ def _engine_from(args):
 
 def command_info(args) -> int:
     import torch
+    from . import models as _models  # noqa: F401  (registers the architectures)
+    from .registry import registered_architectures
     from .csrc import build
     from .engine.engine import PAGE_SIZE
     facts = {"version": __version__, "cuda_available": torch.cuda.is_available(), "torch": torch.__version__,
              "cuda_runtime": torch.version.cuda, "page_size": PAGE_SIZE, "kernel_target": "sm_100a",
-             "kernel_sources": build.CORE_SOURCES + ["attention_mma.cu"]}
+             "kernel_sources": build.CORE_SOURCES + ["attention_mma.cu"],
+             "architectures": list(registered_architectures())}
     if torch.cuda.is_available():
         props = torch.cuda.get_device_properties(0)
         free, total = torch.cuda.mem_get_info(0)

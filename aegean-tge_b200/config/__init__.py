@@ -3,6 +3,8 @@ from .model_spec import LayerSpec, ModelSpec, PartSpec, expected_tensors
 from .qwen2 import ARCHITECTURE as QWEN2_ARCHITECTURE
 from .common import ConfigError, read_config_json
 from .qwen2 import Qwen2Config
+from .lepizen import ARCHITECTURE as LEPIZEN_ARCHITECTURE
+from .lepizen import LepizenConfig
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
-           "Qwen2Config", "QWEN2_ARCHITECTURE", "read_config_json"]
+           "Qwen2Config", "QWEN2_ARCHITECTURE", "LepizenConfig", "LEPIZEN_ARCHITECTURE", "read_config_json"]

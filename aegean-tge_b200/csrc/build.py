@@ -208,10 +208,14 @@ def build_attention(head_dim: int, value_dim: int = 0) -> str:
                   [f"-DTGE_HEAD_DIM={head_dim}", f"-DTGE_VALUE_DIM={value_dim}"])
 
 
-def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
+def build_all(head_dims: Sequence[int] = (16, 32, 64, 128), unequal: Sequence[Sequence[int]] = ((32, 16),)) -> List[str]:
+    """Every library: the runtime, the core, the attention kernels for the usual head sizes and for one pair of
+    unlike key and value sizes (others are compiled when a model with them is first built)."""
     paths = [build_runtime(), build_core()]
     for head_dim in head_dims:
         paths.append(build_attention(head_dim))
+    for head_dim, value_dim in unequal:
+        paths.append(build_attention(head_dim, value_dim))
     return paths
 
 

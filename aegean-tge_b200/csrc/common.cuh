@@ -121,6 +121,19 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { re
 
 // The two usual forms of GELU, in float32.
 __device__ __forceinline__ float gelu_erf(float z) { return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f)); }
+// The erf form for results that are rounded to bfloat16: the normal distribution's tail by the rational
+// approximation erfc(x) ~ t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-x^2), t = 1 / (1 + p x), x >= 0 (absolute
+// error below 1.5e-7, a hundredth of a bfloat16 step of the result), with the fast exponential and division:
+// a dozen instructions where erff takes several dozen.  In a product's epilogue that is the difference between
+// an epilogue hidden behind the next tile and one the tensor cores wait for (a 2,048 x 28,416 x 3,584 product:
+// 267 us plain, 366 us with erff).  Negative arguments take the tail directly, so nothing cancels.
+__device__ __forceinline__ float gelu_erf_fast(float z) {
+  const float x = fabsf(z) * 0.70710678118654752f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, x, 1.0f));
+  const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+  const float half_tail = 0.5f * poly * __expf(-x * x);          // half of erfc(|z| / sqrt 2)
+  return z * (z >= 0.0f ? 1.0f - half_tail : half_tail);
+}
 __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.0f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
 }

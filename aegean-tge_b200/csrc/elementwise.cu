@@ -504,6 +504,102 @@ __global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(
   }
 }
 
+// bfloat16 with every size a multiple of 8 elements and the norm over the whole projection: a token's row is read
+// once in units of 16 bytes that stay in registers between the sums of squares and the scaling, so the row moves
+// through memory once in and once out (and its k and v once more into the pages).
+constexpr int QKN_THREADS = 256;
+constexpr int QKN_UNITS = 12;          // units per thread: rows of up to 256 * 12 * 8 = 24,576 elements
+
+__global__ void __launch_bounds__(QKN_THREADS) qk_norm_kv_store_vec_kernel(
+    __nv_bfloat16* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    float eps, const __nv_bfloat16* __restrict__ v_other, int v_other_stride, const float* __restrict__ blend,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+    int max_pages, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int num_pages, int page_size,
+    int heads, int kv_heads, int head_dim, int value_dim, int store_kv, int* status) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const float lambda = blend != nullptr ? blend[0] : 0.0f;
+  bool store = store_kv != 0;
+  size_t k_base = 0, v_base = 0;
+  if (store) {
+    const int page_index = pos / page_size;
+    const int page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq_of_token[t] * max_pages + page_index] : -1;
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+      store = false;
+    } else {
+      k_base = ((size_t)page * kv_heads * page_size + (pos % page_size)) * head_dim;
+      v_base = ((size_t)page * kv_heads * page_size + (pos % page_size)) * value_dim;
+    }
+  }
+  pdl_wait();
+  const int q_units = heads * head_dim / 8, k_units = kv_heads * head_dim / 8, v_units = kv_heads * value_dim / 8;
+  const int units = q_units + k_units + v_units;
+  uint4* row = reinterpret_cast<uint4*>(qkv + (size_t)t * row_stride);
+  uint4 raw[QKN_UNITS];
+#pragma unroll
+  for (int i = 0; i < QKN_UNITS; ++i) {
+    const int u = threadIdx.x + i * QKN_THREADS;
+    raw[i] = u < units ? row[u] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  float sum_q = 0.0f, sum_k = 0.0f;
+#pragma unroll
+  for (int i = 0; i < QKN_UNITS; ++i) {
+    const int u = threadIdx.x + i * QKN_THREADS;
+    if (u >= q_units + k_units) continue;
+    float f[8];
+    unpack8(raw[i], f);
+    float part = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) part = fmaf(f[e], f[e], part);
+    if (u < q_units) sum_q += part; else sum_k += part;
+  }
+  sum_q = block_sum(sum_q, scratch);
+  sum_k = block_sum(sum_k, scratch);
+  const float f_q = 1.0f / sqrtf(sum_q / (float)(q_units * 8) + eps);
+  const float f_k = 1.0f / sqrtf(sum_k / (float)(k_units * 8) + eps);
+#pragma unroll
+  for (int i = 0; i < QKN_UNITS; ++i) {
+    const int u = threadIdx.x + i * QKN_THREADS;
+    if (u >= units) continue;
+    float f[8];
+    unpack8(raw[i], f);
+    if (u < q_units + k_units) {
+      const bool is_q = u < q_units;
+      const float* weight = is_q ? q_weight : k_weight;
+      if (weight != nullptr) {
+        const float factor = is_q ? f_q : f_k;
+        const int first = (is_q ? u : u - q_units) * 8;
+        const float4 w0 = *reinterpret_cast<const float4*>(weight + first), w1 = *reinterpret_cast<const float4*>(weight + first + 4);
+        f[0] *= factor * w0.x; f[1] *= factor * w0.y; f[2] *= factor * w0.z; f[3] *= factor * w0.w;
+        f[4] *= factor * w1.x; f[5] *= factor * w1.y; f[6] *= factor * w1.z; f[7] *= factor * w1.w;
+        raw[i] = pack8(f);
+        row[u] = raw[i];
+      }
+      if (!is_q && store) {
+        const int e0 = (u - q_units) * 8, h = e0 / head_dim, d = e0 - h * head_dim;
+        *reinterpret_cast<uint4*>(k_pages + k_base + (size_t)h * page_size * head_dim + d) = raw[i];
+      }
+    } else {
+      const int e0 = (u - q_units - k_units) * 8;
+      if (v_other != nullptr) {
+        float o[8];
+        unpack8(*reinterpret_cast<const uint4*>(v_other + (size_t)t * v_other_stride + e0), o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = (1.0f - lambda) * f[e] + lambda * o[e];
+        raw[i] = pack8(f);
+        row[u] = raw[i];
+      }
+      if (store) {
+        const int h = e0 / value_dim, d = e0 - h * value_dim;
+        *reinterpret_cast<uint4*>(v_pages + v_base + (size_t)h * page_size * value_dim + d) = raw[i];
+      }
+    }
+  }
+}
+
 // qkv: [tokens, >= heads*head_dim + kv_heads*(head_dim + value_dim)] rows of [q | k | v], row stride in elements.
 // q_weight / k_weight: float32, heads*head_dim and kv_heads*head_dim long (or head_dim each with per_head), or null.
 // v_other: null, or the other layer's values [tokens, kv_heads*value_dim] with its row stride; blend: device float.
@@ -521,6 +617,17 @@ TGE_API int tge_qk_norm_kv_store(void* qkv, int is_bf16, int row_stride, const f
   TGE_REQUIRE(!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0 && k_pages && v_pages && block_table),
               "qk_norm_kv_store: bad page geometry");
   if (tokens == 0) return 0;
+  const bool aligned16 = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)v_other % 16 == 0) && ((uintptr_t)k_pages % 16 == 0) &&
+                         ((uintptr_t)v_pages % 16 == 0) && ((uintptr_t)q_weight % 16 == 0) && ((uintptr_t)k_weight % 16 == 0);
+  const long long units = ((long long)heads * head_dim + (long long)kv_heads * (head_dim + value_dim)) / 8;
+  if (is_bf16 && !per_head && aligned16 && head_dim % 8 == 0 && value_dim % 8 == 0 && row_stride % 8 == 0 &&
+      v_other_stride % 8 == 0 && units <= (long long)QKN_THREADS * QKN_UNITS) {
+    tge_launch(qk_norm_kv_store_vec_kernel, tokens, QKN_THREADS, 0, stream, (__nv_bfloat16*)qkv, row_stride, q_weight,
+               k_weight, eps, (const __nv_bfloat16*)v_other, v_other_stride, blend, positions, seq_of_token, block_table,
+               max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads,
+               head_dim, value_dim, store_kv, status);
+    return tge_launched("qk_norm_kv_store_vec", 1);
+  }
   if (is_bf16)
     tge_launch(qk_norm_kv_store_kernel<__nv_bfloat16>, tokens, 256, 0, stream, (__nv_bfloat16*)qkv, row_stride, q_weight,
                k_weight, eps, per_head, (const __nv_bfloat16*)v_other, v_other_stride, blend, positions, seq_of_token,

@@ -229,7 +229,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
         if (n_ok && m < p.m_tok) p.partial[((size_t)split * p.m_tok + m) * p.n_w + n] = v;
       } else if (n_ok && m < p.m_tok) {
         if (p.epilogue >= GEMM_GELU) {
-          if (n >= p.act_from) v = p.epilogue == GEMM_GELU ? gelu_erf(v) : gelu_tanh(v);
+          if (n >= p.act_from) v = p.epilogue == GEMM_GELU ? gelu_erf_fast(v) : gelu_tanh(v);
           reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(v);
         } else if (p.epilogue == GEMM_STORE) {
           reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(p.alpha * v);
@@ -657,7 +657,7 @@ __global__ void splitk_epilogue_kernel(const float* __restrict__ partial, const 
     v *= row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, m);
     if (bias) v += bias[n];
     if (epilogue >= GEMM_GELU) {
-      if (n >= act_from) v = epilogue == GEMM_GELU ? gelu_erf(v) : gelu_tanh(v);
+      if (n >= act_from) v = epilogue == GEMM_GELU ? gelu_erf_fast(v) : gelu_tanh(v);
       reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
       continue;
     }
@@ -1190,6 +1190,105 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
   }
 }
 
+// A layer whose q and k are RMS-normalised over a token's whole projection (no rotation), whose values may be
+// blended with an earlier layer's, and beside whose q/k/v rows the product may carry a feed-forward's up rows:
+// weight rows [q | k | v | up].  Block y == 0 of a token adds the partial sums of its q, k and v columns, keeps
+// them in float32, works out the two sums of squares, writes normalised q and k and (blended) v into the qkv
+// buffer and k and v into their pages; blocks y >= 1 add the partial sums of a slice of the up columns and write
+// their GELU.  One kernel where the separate path runs two sums of partial products and the norm-and-store.
+constexpr int QKV_ACT_THREADS = 512;
+constexpr int QKV_ACT_SLICE = 2048;              // up columns per block
+
+__global__ void __launch_bounds__(QKV_ACT_THREADS)
+splitk_qkv_norm_act_store_kernel(const float* __restrict__ partial, int m_tok, int n_w, int splits,
+                                 __nv_bfloat16* __restrict__ qkv, long long ld_qkv, __nv_bfloat16* __restrict__ act_out,
+                                 long long ld_act, int activation, const float* __restrict__ q_weight,
+                                 const float* __restrict__ k_weight, float eps, const __nv_bfloat16* __restrict__ v_other,
+                                 long long ld_other, const float* __restrict__ blend, const int* __restrict__ positions,
+                                 const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int max_pages,
+                                 __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int num_pages,
+                                 int page_size, int heads, int kv_heads, int head_dim, int value_dim, int store_kv,
+                                 int* status, const float* __restrict__ ss, int ss_slices, int ss_width, float ss_eps) {
+  extern __shared__ float row_values[];
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const size_t plane = (size_t)m_tok * n_w;
+  const int n_q = heads * head_dim, n_k = kv_heads * head_dim, n_v = kv_heads * value_dim;
+  const int n_qkv = n_q + n_k + n_v;
+  if (blockIdx.y > 0) {
+    const int first = n_qkv + ((int)blockIdx.y - 1) * QKV_ACT_SLICE;
+    const int last = min(first + QKV_ACT_SLICE, n_w);
+    pdl_wait();
+    const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, t);
+    for (int c = first + threadIdx.x; c < last; c += QKV_ACT_THREADS) {
+      const float* src = partial + (size_t)t * n_w + c;
+      float acc = 0.0f;
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) acc += src[s * plane];
+      acc *= factor;
+      act_out[(size_t)t * ld_act + (c - n_qkv)] = __float2bfloat16_rn(activation == GEMM_GELU ? gelu_erf_fast(acc) : gelu_tanh(acc));
+    }
+    return;
+  }
+  // what the step was given and the model's constants: read while the product still runs
+  const int pos = positions[t];
+  const float lambda = blend != nullptr ? blend[0] : 0.0f;
+  int page = -1, slot = 0;
+  if (store_kv) {
+    const int seq = seq_of_token[t];
+    const int page_index = pos / page_size;
+    page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
+    slot = pos - page_index * page_size;
+  }
+  pdl_wait();
+  const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, t);
+  float sum_q = 0.0f, sum_k = 0.0f;
+  for (int c = threadIdx.x; c < n_qkv; c += QKV_ACT_THREADS) {
+    const float* src = partial + (size_t)t * n_w + c;
+    float acc = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < splits; ++s) acc += src[s * plane];
+    acc *= factor;
+    row_values[c] = acc;
+    if (c < n_q) sum_q = fmaf(acc, acc, sum_q);
+    else if (c < n_q + n_k) sum_k = fmaf(acc, acc, sum_k);
+  }
+  sum_q = block_sum(sum_q, scratch);
+  sum_k = block_sum(sum_k, scratch);
+  const float f_q = q_weight != nullptr ? 1.0f / sqrtf(sum_q / (float)n_q + eps) : 1.0f;
+  const float f_k = k_weight != nullptr ? 1.0f / sqrtf(sum_k / (float)n_k + eps) : 1.0f;
+  bool store = store_kv != 0;
+  if (store && (page < 0 || page >= num_pages)) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+    store = false;
+  }
+  __nv_bfloat16* row = qkv + (size_t)t * ld_qkv;
+  for (int c = threadIdx.x; c < n_qkv; c += QKV_ACT_THREADS) {       // each thread the columns it summed itself
+    float v = row_values[c];
+    if (c < n_q) {
+      row[c] = __float2bfloat16_rn(q_weight != nullptr ? v * f_q * q_weight[c] : v);
+    } else if (c < n_q + n_k) {
+      const int i = c - n_q;
+      const __nv_bfloat16 out = __float2bfloat16_rn(k_weight != nullptr ? v * f_k * k_weight[i] : v);
+      row[c] = out;
+      if (store) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        k_pages[(((size_t)page * kv_heads + h) * page_size + slot) * head_dim + d] = out;
+      }
+    } else {
+      const int i = c - n_q - n_k;
+      if (v_other != nullptr) v = (1.0f - lambda) * v + lambda * __bfloat162float(v_other[(size_t)t * ld_other + i]);
+      const __nv_bfloat16 out = __float2bfloat16_rn(v);
+      row[c] = out;
+      if (store) {
+        const int h = i / value_dim, d = i - h * value_dim;
+        v_pages[(((size_t)page * kv_heads + h) * page_size + slot) * value_dim + d] = out;
+      }
+    }
+  }
+}
+
 // The add+norm kernel without the norm's factor: the stream takes the sums, the next product's input is
 // stream * weight, and each block leaves the sum of squares of its slice of the row; whoever multiplies that
 // input works the factor out of the slices' sums (always in slice order) and applies it to its result.  No
@@ -1333,4 +1432,49 @@ TGE_API int tge_gemm_tcgen05_qkv_rope(const void* x, long long ldx, const void* 
              (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim, status,
              x_ss, x_ss_slices, x_ss_width, x_ss_eps);
   return tge_launched("splitk_qkv_rope_store", 2);
+}
+
+// The fused q/k/v (+ up) product of a layer that normalises q and k over their whole projections: weight rows
+// [q | k | v | up], N = heads*head_dim + kv_heads*(head_dim + value_dim) + up rows.  qkv (bf16 [M, >= q+k+v]) gets
+// normalised q and k and the (blended) values, the pages get k and v, act_out (bf16 [M, >= up rows], null without up
+// rows) gets GELU(up) in the erf (activation 4) or tanh (5) form.  q_weight / k_weight null: no norm of that
+// projection.  Same conditions and return codes as tge_gemm_tcgen05_add_norm.
+TGE_API int tge_gemm_tcgen05_qkv_norm_act(const void* x, long long ldx, const void* w, long long ldw, void* qkv,
+                                          long long ld_qkv, void* act_out, long long ld_act, int activation, int M, int N,
+                                          int K, const float* q_weight, const float* k_weight, float eps,
+                                          const void* v_other, long long ld_other, const float* blend,
+                                          const int* positions, const int* seq_of_token, const int* block_table,
+                                          int max_pages, void* k_pages, void* v_pages, int num_pages, int page_size,
+                                          int heads, int kv_heads, int head_dim, int value_dim, int store_kv,
+                                          float* scratch, long long scratch_floats, int* status, const float* x_ss,
+                                          int x_ss_slices, int x_ss_width, float x_ss_eps, cudaStream_t stream) {
+  TGE_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm+qk-norm: bad sizes M=%d N=%d K=%d", M, N, K);
+  const long long n_qkv = (long long)heads * head_dim + (long long)kv_heads * (head_dim + value_dim);
+  TGE_REQUIRE(heads > 0 && kv_heads > 0 && head_dim > 0 && value_dim > 0 && n_qkv <= N,
+              "gemm+qk-norm: %d weight rows do not hold q, k and v", N);
+  TGE_REQUIRE((n_qkv == N) == (act_out == nullptr), "gemm+qk-norm: rows beyond q, k and v need an output, and only they");
+  TGE_REQUIRE(activation == GEMM_GELU || activation == GEMM_GELU_TANH || act_out == nullptr, "gemm+qk-norm: unknown activation %d", activation);
+  TGE_REQUIRE((v_other == nullptr) == (blend == nullptr), "gemm+qk-norm: a blend needs both the other values and its weight");
+  TGE_REQUIRE(status != nullptr && (!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0)), "gemm+qk-norm: bad arguments");
+  TGE_REQUIRE(eps > 0.0f || (q_weight == nullptr && k_weight == nullptr), "gemm+qk-norm: eps must be positive");
+  if (M == 0) return 0;
+  if (M > FUSED_MAX_TOKENS || (size_t)n_qkv * sizeof(float) > 200 * 1024 || scratch == nullptr) return TGE_UNSUPPORTED;
+  int splits = 0;
+  int rc = launch_product(x, ldx, w, ldw, nullptr, qkv, ld_qkv, M, N, K, GEMM_STORE, scratch, scratch_floats, 0, 0, true,
+                          status, stream, &splits);
+  if (rc != 1) return rc;
+  const size_t smem = (size_t)n_qkv * sizeof(float);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t err = cudaFuncSetAttribute(splitk_qkv_norm_act_store_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    TGE_REQUIRE(err == cudaSuccess, "gemm+qk-norm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
+    configured = smem;
+  }
+  const int act_blocks = (int)((N - n_qkv + QKV_ACT_SLICE - 1) / QKV_ACT_SLICE);
+  tge_launch(splitk_qkv_norm_act_store_kernel, dim3(M, 1 + act_blocks), QKV_ACT_THREADS, smem, stream,
+             (const float*)scratch, M, N, splits, (__nv_bfloat16*)qkv, ld_qkv, (__nv_bfloat16*)act_out, ld_act, activation,
+             q_weight, k_weight, eps, (const __nv_bfloat16*)v_other, ld_other, blend, positions, seq_of_token, block_table,
+             max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim,
+             value_dim, store_kv, status, x_ss, x_ss_slices, x_ss_width, x_ss_eps);
+  return tge_launched("splitk_qkv_norm_act_store", 2);
 }

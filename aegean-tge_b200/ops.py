@@ -81,6 +81,11 @@ def core() -> ctypes.CDLL:
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                                     _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                     _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr])
+        _declare(lib, "tge_gemm_tcgen05_qkv_norm_act", [_c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_int,
+                                                        _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ll,
+                                                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                                                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ll,
+                                                        _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr])
         lib.tge_gemm_tcgen05_pair_mode.argtypes = [_c_int]
         lib.tge_gemm_tcgen05_pair_mode.restype = None
         lib.tge_gemm_tcgen05_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
@@ -381,6 +386,77 @@ def qk_norm_kv_store(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weig
                                     positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table), max_pages,
                                     _ptr(k_pages), _ptr(v_pages), num_pages, page_size, tokens, heads, kv_heads,
                                     head_dim, value_dim, int(store), status_word().data_ptr(), _stream()), lib)
+
+
+def linear_qkv_norm_act_store(x, w: torch.Tensor, heads: int, kv_heads: int, head_dim: int, value_dim: int,
+                              q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                              positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: Optional[torch.Tensor],
+                              k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
+                              v_other: Optional[torch.Tensor] = None, blend: Optional[torch.Tensor] = None,
+                              act_out: Optional[torch.Tensor] = None, activation: int = GEMM_GELU) -> Optional[torch.Tensor]:
+    """For a small bfloat16 batch, the q/k/v product of a layer that normalises q and k over their whole
+    projections, with what follows it in one kernel: the product's partial sums are added, q and k normalised
+    (float32), the values blended with ``v_other`` and k and v stored (as :func:`qk_norm_kv_store` does).  The
+    weight may carry more rows below q, k and v, a feed-forward's up rows: their GELU goes to ``act_out``
+    [T, up rows] (dense rows, any row stride).  Returns the qkv buffer [T, q | k | v], or None when the batch or
+    the shape is not one for this path: the caller then runs the separate kernels."""
+    deferred = x if isinstance(x, DeferredRows) else None
+    if deferred is not None:
+        x = deferred.rows
+    M, K = x.shape
+    N = w.shape[0]
+    n_qkv = heads * head_dim + kv_heads * (head_dim + value_dim)
+    if not (x.dtype == torch.bfloat16 and USE_TCGEN05 and M <= FUSED_MAX_TOKENS) or (N > n_qkv) != (act_out is not None):
+        return None
+    if deferred is not None and M > DEFER_MAX_TOKENS:
+        return None
+    _want(x, "linear input", torch.bfloat16, contiguous=False)
+    _want(w, "linear weight", torch.bfloat16, contiguous=False)
+    for name, t in (("positions", positions), ("seq_of_token", seq_of_token)):
+        _want(t, name, torch.int32)
+    for name, t, count in (("q norm weight", q_weight, heads * head_dim), ("k norm weight", k_weight, kv_heads * head_dim)):
+        if t is not None:
+            _want(t, name, torch.float32)
+            if t.numel() != count:
+                raise KernelError(f"{name} has {t.numel()} elements, the projection {count}")
+    store = k_pages is not None
+    num_pages = page_size = max_pages = 0
+    if store:
+        _want(k_pages, "k pages", torch.bfloat16)
+        _want(v_pages, "v pages", torch.bfloat16)
+        _want(block_table, "block table", torch.int32)
+        num_pages, _, page_size, _ = k_pages.shape
+        if (tuple(k_pages.shape) != (num_pages, kv_heads, page_size, head_dim)
+                or tuple(v_pages.shape) != (num_pages, kv_heads, page_size, value_dim) or w.shape[1] != K):
+            raise KernelError("linear_qkv_norm_act_store: shapes do not fit")
+        max_pages = block_table.shape[1]
+    other_stride = act_stride = 0
+    if (v_other is None) != (blend is None):
+        raise KernelError("linear_qkv_norm_act_store: a blend needs the other values and its weight")
+    if v_other is not None:
+        _want(v_other, "other values", torch.bfloat16, contiguous=False)
+        _want(blend, "blend weight", torch.float32)
+        other_stride = _rows_2d(v_other, "other values")
+        if tuple(v_other.shape) != (M, kv_heads * value_dim):
+            raise KernelError("linear_qkv_norm_act_store: the other values do not fit")
+    if act_out is not None:
+        _want(act_out, "activated rows", torch.bfloat16, contiguous=False)
+        act_stride = _rows_2d(act_out, "activated rows")
+        if tuple(act_out.shape) != (M, N - n_qkv):
+            raise KernelError("linear_qkv_norm_act_store: the activated rows do not fit")
+    lib = core()
+    need = max(lib.tge_gemm_tcgen05_scratch_floats(M, N, K), M * N)
+    scratch = scratch_floats(need)
+    qkv = torch.empty((M, n_qkv), dtype=torch.bfloat16, device=x.device)
+    rc = lib.tge_gemm_tcgen05_qkv_norm_act(x.data_ptr(), _rows_2d(x, "linear input"), w.data_ptr(), _rows_2d(w, "linear weight"),
+                                           qkv.data_ptr(), n_qkv, _ptr(act_out), act_stride, int(activation), M, N, K,
+                                           _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(v_other), other_stride,
+                                           _ptr(blend), positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table),
+                                           max_pages, _ptr(k_pages), _ptr(v_pages), num_pages, page_size, heads, kv_heads,
+                                           head_dim, value_dim, int(store), scratch.data_ptr(), scratch.numel(),
+                                           status_word().data_ptr(),
+                                           *(_NO_FACTOR if deferred is None else deferred.factor_args()), _stream())
+    return None if _check(rc, lib) == UNSUPPORTED else qkv
 
 
 def soft_cap(z: torch.Tensor, cap: float) -> torch.Tensor:

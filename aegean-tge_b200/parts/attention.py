@@ -87,6 +87,8 @@ class GQAttention(Mixer):
         self.k_norm_w: Optional[torch.Tensor] = None
         self.sink: Optional[torch.Tensor] = None
         self.mix_w: Optional[torch.Tensor] = None
+        # q/k/v rows and, below them, rows that a block placed there (a feed-forward's up rows), in one tensor
+        self.w_shared: Optional[torch.Tensor] = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.b_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
@@ -140,15 +142,32 @@ class GQAttention(Mixer):
         return PagedCacheSpec(entries=(("k", (self.kv_heads, self.head_dim)), ("v", (self.kv_heads, self.value_dim))),
                               window=None if self.window is None else int(self.window))
 
+    def share_input_projection(self, rows: torch.Tensor) -> Optional[torch.Tensor]:
+        """A block offers the rows of another product over the same input (a feed-forward's up weight) to be
+        multiplied together with q, k and v.  A mixer whose small-batch kernel can carry them (whole-projection
+        q/k norm, no rotation, no biases) puts them below its own rows in one tensor and returns the view that now
+        holds them (the caller uses it in place of its copy); None: it cannot."""
+        if self.plain or self.rotates or self.qkv_bias or (self.qk_norm is not None and self.qk_norm[0] != "projection"):
+            return None
+        if self.w_qkv is None or rows.dtype != self.w_qkv.dtype or rows.shape[1] != self.hidden:
+            return None
+        count = self.w_qkv.shape[0]
+        self.w_shared = torch.cat([self.w_qkv, rows], dim=0).contiguous()
+        self.w_qkv = self.w_shared[:count]
+        return self.w_shared[count:]
+
     def attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Everything up to, not including, the output projection: [T, heads*value_dim] (into ``out`` if given)."""
+               out: Optional[torch.Tensor] = None, beside=None):
+        """Everything up to, not including, the output projection: [T, heads*value_dim] (into ``out`` if given).
+
+        ``beside``: (output view, epilogue) for the rows that :meth:`share_input_projection` took in; the result is
+        then a pair (rows, whether the shared rows were multiplied and activated here)."""
         ops = self.ops
         k_pages, v_pages = cache.paged["k"], cache.paged["v"]
         table = ctx.block_tables[cache.group]
         tables = self.position.rotary_tables()
+        did_beside = False
         if not self.plain:
-            qkv = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
             other = blend = None
             if self.value_mix == "blend":
                 if self.value_mix_key not in ctx.scratch:
@@ -158,10 +177,22 @@ class GQAttention(Mixer):
             q_w, k_w, eps, per_head = self.q_norm_w, self.k_norm_w, 1.0, False
             if self.qk_norm is not None:
                 per_head, eps = self.qk_norm[0] == "head", self.qk_norm[1]
-            ops.qk_norm_kv_store(qkv, q_w, k_w, eps, per_head, ctx.positions, ctx.seq_of_token,
-                                 table if store_here else None, k_pages if store_here else None,
-                                 v_pages if store_here else None, self.heads, self.kv_heads, self.head_dim,
-                                 self.value_dim, v_other=other, blend=blend)
+            qkv = None
+            if not per_head and not self.rotates and self.b_qkv is None:
+                # small batches: the product's partial sums are added, normalised, blended and stored by one kernel
+                shared = beside is not None and self.w_shared is not None
+                qkv = ops.linear_qkv_norm_act_store(
+                    h, self.w_shared if shared else self.w_qkv, self.heads, self.kv_heads, self.head_dim, self.value_dim,
+                    q_w, k_w, eps, ctx.positions, ctx.seq_of_token, table if store_here else None,
+                    k_pages if store_here else None, v_pages if store_here else None, v_other=other, blend=blend,
+                    act_out=beside[0] if shared else None, activation=beside[1] if shared else ops.GEMM_GELU)
+                did_beside = shared and qkv is not None
+            if qkv is None:
+                qkv = ops.linear(h, self.w_qkv, self.b_qkv, ops.GEMM_STORE)
+                ops.qk_norm_kv_store(qkv, q_w, k_w, eps, per_head, ctx.positions, ctx.seq_of_token,
+                                     table if store_here else None, k_pages if store_here else None,
+                                     v_pages if store_here else None, self.heads, self.kv_heads, self.head_dim,
+                                     self.value_dim, v_other=other, blend=blend)
             if self.value_mix == "first":
                 ctx.scratch[self.value_mix_key] = qkv[:, self.q_dim + self.kv_dim:self.q_dim + self.kv_dim + self.v_dim]
             if self.rotates:
@@ -195,14 +226,15 @@ class GQAttention(Mixer):
             ops.rope_kv_store(qkv, cos, sin, rotary, ctx.positions, ctx.seq_of_token, table,
                               k_pages if cache.owner else None, v_pages if cache.owner else None,
                               self.heads, self.kv_heads, self.head_dim)
-        return ops.attention(qkv[:, :self.q_dim], k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions,
-                             ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads,
-                             self.kv_heads, self.head_dim, self.scale, window=int(self.window or 0),
-                             split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
-                             decode_prefix=ctx.decode_prefix, sink=self.sink, out=out)
+        a = ops.attention(qkv[:, :self.q_dim], k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions,
+                          ctx.seq_of_token, ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads,
+                          self.kv_heads, self.head_dim, self.scale, window=int(self.window or 0),
+                          split_tokens=ctx.attn_split_tokens, typical_ctx_len=ctx.typical_ctx_len,
+                          decode_prefix=ctx.decode_prefix, sink=self.sink, out=out)
+        return a if beside is None else (a, did_beside)
 
-    def inner(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return self.attend(h, ctx, cache, out=out)
+    def inner(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None, beside=None):
+        return self.attend(h, ctx, cache, out=out, beside=beside)
 
     def output_projection(self):
         return self.w_o, self.b_o

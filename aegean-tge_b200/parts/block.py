@@ -55,6 +55,7 @@ class ParallelBlock(Block):
         self.w_out: Optional[torch.Tensor] = None
         self.b_out: Optional[torch.Tensor] = None
         self.split = 0
+        self.shared_input = False      # the feed-forward's up rows lie below the mixer's q/k/v rows
 
     def loaded(self) -> None:
         """Concatenates the two output weights along their columns, once the parts have theirs."""
@@ -74,6 +75,15 @@ class ParallelBlock(Block):
         # the parts' own copies are not needed again: this block runs their last products
         self.mixer.w_o = None
         self.feed_forward.w_down = None
+        # the two first products read the same rows too: a mixer that can carry the up rows through its own
+        # small-batch kernel takes them in (they stay one tensor; both parts keep views of it)
+        share = getattr(self.mixer, "share_input_projection", None)
+        adopt = getattr(self.feed_forward, "adopt_input_projection", None)
+        if share is not None and adopt is not None:
+            view = share(self.feed_forward.input_projection())
+            if view is not None:
+                adopt(view)
+                self.shared_input = True
         if b_a is not None or b_f is not None:
             zero = torch.zeros(w_a.shape[0], dtype=torch.float32, device=w_a.device)
             self.b_out = ((b_a if b_a is not None else zero) + (b_f if b_f is not None else zero)).contiguous()
@@ -92,9 +102,15 @@ class ParallelBlock(Block):
             return None
         tokens = x.shape[0]
         inner = torch.empty((tokens, self.w_out.shape[1]), dtype=self.env.dtype, device=x.device)
-        if self.feed_forward is not None:
-            self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
-        self.mixer.inner(h, ctx, cache, out=inner[:, :self.split])
+        if self.shared_input:
+            beside = (inner[:, self.split:], self.feed_forward.epilogue())
+            _rows, done = self.mixer.inner(h, ctx, cache, out=inner[:, :self.split], beside=beside)
+            if not done:
+                self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
+        else:
+            if self.feed_forward is not None:
+                self.feed_forward.inner(h, ctx, out=inner[:, self.split:])
+            self.mixer.inner(h, ctx, cache, out=inner[:, :self.split])
         fused = next_norm.fusable() if next_norm is not None else None
         if fused is not None:
             return ops.linear_add_norm(inner, self.w_out, self.b_out, x, fused[0], fused[1], self.env.dtype,

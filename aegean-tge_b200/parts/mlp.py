@@ -95,9 +95,18 @@ class DenseMLP(FeedForward):
     def flops(self, tokens: int, pairs: float) -> float:
         return 2.0 * tokens * 2 * self.inner_size * self.hidden
 
+    def epilogue(self) -> int:
+        return self.ops.GEMM_GELU if self.activation == "gelu" else self.ops.GEMM_GELU_TANH
+
+    def input_projection(self) -> torch.Tensor:
+        return self.w_up
+
+    def adopt_input_projection(self, view: torch.Tensor) -> None:
+        """The up rows now live inside a tensor that another part shares (same values): use that copy."""
+        self.w_up = view
+
     def inner(self, h, ctx: StepContext, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        epilogue = self.ops.GEMM_GELU if self.activation == "gelu" else self.ops.GEMM_GELU_TANH
-        return self.ops.linear(h, self.w_up, None, epilogue, out=out)
+        return self.ops.linear(h, self.w_up, None, self.epilogue(), out=out)
 
     def output_projection(self):
         return self.w_down, None

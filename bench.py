@@ -14,6 +14,12 @@ decode step against HBM bandwidth.  ``points`` holds decode at batch 1 and 64
 portion), the same figures with the engine's default pages of 64 tokens, long
 contexts, and the 14B and 32B shapes.  This engine runs on one GPU: for --gpus
 above 1 it says so and exits with 2.
+
+    python bench.py --compare lepizen [--compare-sizes 7b,14b,1.5b] [--steps K]
+
+is another measurement and leaves the one above alone: the Lepizen design beside the Qwen2 design at equal
+width, heads, layers, vocabulary and parameter count, at sizes of real models' layers (random weights), prefill
+and decode, with the kernels of one step of each.  It prints one JSON line {"compare": ...}.
 """
 import argparse
 import json
@@ -141,6 +147,35 @@ def prefill_record(run):
             "sustained_value": round(run["tokens"] / (run["sustained_ms"] * 1e-3), 1), "mean3_ms": round(run["ms"], 3)}
 
 
+# layer shapes of the Qwen2.5 family: width, heads, kv heads, head size, gated inner width
+COMPARE_SIZES = {"1.5b": (1536, 12, 2, 128, 8960), "7b": (3584, 28, 4, 128, 18944), "14b": (5120, 40, 8, 128, 13824)}
+
+
+def compare(args) -> int:
+    """`--compare lepizen`: both designs at each size, one JSON line."""
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    from aegean_tge_b200 import ops, peaks
+    from aegean_tge_b200.bench_tools import compare_designs, paired_configs
+    sizes = [s.strip() for s in args.compare_sizes.split(",") if s.strip()]
+    for size in sizes:
+        if size not in COMPARE_SIZES:
+            print(f"bench.py: --compare-sizes knows {', '.join(COMPARE_SIZES)}, not '{size}'")
+            return 2
+    peak, source = peaks.load()
+    out = {"designs": ["qwen2", args.compare], "layers": args.compare_layers, "prompt": PROMPT, "dtype": "bf16",
+           "data": "synthetic: random weights seed 0, uniform random token ids", "peaks": peak, "peaks_source": source,
+           "sizes": {}}
+    for size in sizes:
+        width, heads, kv_heads, head_dim, inner = COMPARE_SIZES[size]
+        configs = paired_configs(width, heads, kv_heads, head_dim, inner, args.compare_layers, CONFIG_7B["vocab_size"])
+        out["sizes"][size] = compare_designs(configs, prompt_len=PROMPT, steps=min(args.steps, 32), warmup=max(args.warmup, 3))
+    ops.check_status()
+    print(json.dumps({"compare": out}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -150,9 +185,14 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=CONFIG_7B["num_hidden_layers"],
                         help="fewer layers than the model has, if memory or time needs it (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="the headline only: no points")
+    parser.add_argument("--compare", choices=["lepizen"], help="instead of the headline: this design beside Qwen2 at equal size")
+    parser.add_argument("--compare-sizes", default="7b,14b,1.5b", help="which of 1.5b, 7b, 14b (layer shapes), with commas")
+    parser.add_argument("--compare-layers", type=int, default=8, help="layers of each model in --compare")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.compare:
+        return compare(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -72,3 +72,4 @@ def test_info_json_needs_no_gpu():
     assert out.returncode == 0
     facts = json.loads(out.stdout)
     assert facts["kernel_target"] == "sm_100a" and facts["page_size"] == 64
+    assert "Lepizen" in facts["architectures"] and "Qwen2ForCausalLM" in facts["architectures"]

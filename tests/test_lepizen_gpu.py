@@ -264,6 +264,58 @@ def test_projection_norm_blend_and_store(ops, dtype, per_head, heads, kv_heads, 
         begin += n
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,width,up_rows", [(6, 2, 48, 16, 256, 0), (3, 1, 32, 64, 128, 200), (8, 2, 64, 64, 512, 2304),
+                                                                 (28, 4, 128, 128, 512, 4104)])
+@pytest.mark.parametrize("q_lens,starts", [([1, 1, 1], [30, 47, 0]), ([5, 1, 20], [30, 47, 0]), ([70, 58], [3, 16])])
+@pytest.mark.parametrize("blend,deferred", [(None, False), (0.37, False), (0.6, True)])
+def test_small_batch_product_with_norm_blend_store_and_gelu(ops, heads, kv_heads, dim, vdim, width, up_rows, q_lens, starts,
+                                                             blend, deferred):
+    """One product over the rows [q | k | v | up] whose partial sums one kernel adds, normalises, blends, stores and
+    activates: against the same steps in float64, also from rows that still lack their norm factor."""
+    page_size, eps = 16, 2e-4
+    lengths = [s + n for s, n in zip(starts, q_lens)]
+    k_pages, _, table, _, _ = paged_cache(lengths, kv_heads, dim, page_size, torch.bfloat16, DEV, seed=3)
+    _, v_pages, _, _, _ = paged_cache(lengths, kv_heads, vdim, page_size, torch.bfloat16, DEV, seed=3)
+    positions, seq_of_token, _, _ = batch_index(q_lens, starts, DEV)
+    T = sum(q_lens)
+    gen = torch.Generator().manual_seed(12)
+    nq, nk, nv = heads * dim, kv_heads * dim, kv_heads * vdim
+    x = torch.randn(T, width, generator=gen).to(torch.bfloat16)
+    w = (torch.randn(nq + nk + nv + up_rows, width, generator=gen) / math.sqrt(width)).to(torch.bfloat16)
+    other = torch.randn(T, nv + 8, generator=gen).to(torch.bfloat16)
+    qw, kw = torch.rand(nq, generator=gen) + 0.5, torch.rand(nk, generator=gen) + 0.5
+    lam = None if blend is None else torch.tensor([blend], dtype=torch.float32, device=DEV)
+    act = torch.zeros(T, up_rows + 8, dtype=torch.bfloat16, device=DEV) if up_rows else None
+    given, factor = x.to(DEV), torch.ones(T, 1, dtype=torch.float64)
+    if deferred:
+        sums = torch.rand(3, T, generator=gen) * width
+        given = ops.DeferredRows(x.to(DEV), sums.to(DEV), width, 1e-5)
+        factor = (1.0 / torch.sqrt(sums.double().sum(0) / width + 1e-5))[:, None]
+    qkv = ops.linear_qkv_norm_act_store(given, w.to(DEV), heads, kv_heads, dim, vdim, qw.to(DEV), kw.to(DEV), eps, positions,
+                                        seq_of_token, table, k_pages, v_pages,
+                                        v_other=None if blend is None else other.to(DEV)[:, :nv], blend=lam,
+                                        act_out=None if act is None else act[:, :up_rows], activation=ops.GEMM_GELU)
+    ops.check_status()
+    assert qkv is not None and tuple(qkv.shape) == (T, nq + nk + nv)
+    z = (x.double() @ w.double().T * factor).numpy()
+    tol = KERNEL_TOL[torch.bfloat16]
+    assert rel_error(qkv[:, :nq], torch.from_numpy(plain.rms_norm(z[:, :nq], qw.numpy(), eps))) < tol
+    assert rel_error(qkv[:, nq:nq + nk], torch.from_numpy(plain.rms_norm(z[:, nq:nq + nk], kw.numpy(), eps))) < tol
+    v_ref = plain.blend_values(z[:, nq + nk:nq + nk + nv], None if blend is None else other.float().numpy()[:, :nv], blend or 0.0)
+    assert rel_error(qkv[:, nq + nk:], torch.from_numpy(v_ref)) < tol
+    if up_rows:
+        assert rel_error(act[:, :up_rows], torch.from_numpy(plain.gelu_erf(z[:, nq + nk + nv:]))) < tol
+        assert float(act[:, up_rows:].abs().max()) == 0.0
+    begin = 0
+    for s, (n, start) in enumerate(zip(q_lens, starts)):
+        for i in range(n):
+            pos = start + i
+            page = int(table[s, pos // page_size])
+            assert torch.equal(k_pages[page, :, pos % page_size, :].reshape(-1), qkv[begin + i, nq:nq + nk])
+            assert torch.equal(v_pages[page, :, pos % page_size, :].reshape(-1), qkv[begin + i, nq + nk:])
+        begin += n
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(9, 260, 328), (150, 384, 704), (3, 97, 100), (700, 520, 264)])
 @pytest.mark.parametrize("simt", [False, True])
