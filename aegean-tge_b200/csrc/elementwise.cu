@@ -508,8 +508,11 @@ __global__ void __launch_bounds__(256) qk_norm_kv_store_kernel(
 // once in units of 16 bytes that stay in registers between the sums of squares and the scaling, so the row moves
 // through memory once in and once out (and its k and v once more into the pages).
 constexpr int QKN_THREADS = 256;
-constexpr int QKN_UNITS = 12;          // units per thread: rows of up to 256 * 12 * 8 = 24,576 elements
+constexpr int QKN_UNITS = 12;          // most units per thread: rows of up to 256 * 12 * 8 = 24,576 elements
 
+// UNITS: units of 16 bytes a thread holds (2, 4, 8 or 12, the least that covers the row: fewer registers, more
+// blocks on an SM; with 12 for every row a 2,048-token step took 28 us where the rotate-and-store kernel takes 10).
+template <int UNITS>
 __global__ void __launch_bounds__(QKN_THREADS) qk_norm_kv_store_vec_kernel(
     __nv_bfloat16* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     float eps, const __nv_bfloat16* __restrict__ v_other, int v_other_stride, const float* __restrict__ blend,
@@ -538,15 +541,15 @@ __global__ void __launch_bounds__(QKN_THREADS) qk_norm_kv_store_vec_kernel(
   const int q_units = heads * head_dim / 8, k_units = kv_heads * head_dim / 8, v_units = kv_heads * value_dim / 8;
   const int units = q_units + k_units + v_units;
   uint4* row = reinterpret_cast<uint4*>(qkv + (size_t)t * row_stride);
-  uint4 raw[QKN_UNITS];
+  uint4 raw[UNITS];
 #pragma unroll
-  for (int i = 0; i < QKN_UNITS; ++i) {
+  for (int i = 0; i < UNITS; ++i) {
     const int u = threadIdx.x + i * QKN_THREADS;
     raw[i] = u < units ? row[u] : make_uint4(0u, 0u, 0u, 0u);
   }
   float sum_q = 0.0f, sum_k = 0.0f;
 #pragma unroll
-  for (int i = 0; i < QKN_UNITS; ++i) {
+  for (int i = 0; i < UNITS; ++i) {
     const int u = threadIdx.x + i * QKN_THREADS;
     if (u >= q_units + k_units) continue;
     float f[8];
@@ -561,7 +564,7 @@ __global__ void __launch_bounds__(QKN_THREADS) qk_norm_kv_store_vec_kernel(
   const float f_q = 1.0f / sqrtf(sum_q / (float)(q_units * 8) + eps);
   const float f_k = 1.0f / sqrtf(sum_k / (float)(k_units * 8) + eps);
 #pragma unroll
-  for (int i = 0; i < QKN_UNITS; ++i) {
+  for (int i = 0; i < UNITS; ++i) {
     const int u = threadIdx.x + i * QKN_THREADS;
     if (u >= units) continue;
     float f[8];
@@ -622,10 +625,17 @@ TGE_API int tge_qk_norm_kv_store(void* qkv, int is_bf16, int row_stride, const f
   const long long units = ((long long)heads * head_dim + (long long)kv_heads * (head_dim + value_dim)) / 8;
   if (is_bf16 && !per_head && aligned16 && head_dim % 8 == 0 && value_dim % 8 == 0 && row_stride % 8 == 0 &&
       v_other_stride % 8 == 0 && units <= (long long)QKN_THREADS * QKN_UNITS) {
-    tge_launch(qk_norm_kv_store_vec_kernel, tokens, QKN_THREADS, 0, stream, (__nv_bfloat16*)qkv, row_stride, q_weight,
-               k_weight, eps, (const __nv_bfloat16*)v_other, v_other_stride, blend, positions, seq_of_token, block_table,
-               max_pages, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads,
-               head_dim, value_dim, store_kv, status);
+    const int per_thread = (int)((units + QKN_THREADS - 1) / QKN_THREADS);
+    auto launch = [&](auto kernel) {
+      tge_launch(kernel, tokens, QKN_THREADS, 0, stream, (__nv_bfloat16*)qkv, row_stride, q_weight, k_weight, eps,
+                 (const __nv_bfloat16*)v_other, v_other_stride, blend, positions, seq_of_token, block_table, max_pages,
+                 (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, page_size, heads, kv_heads, head_dim,
+                 value_dim, store_kv, status);
+    };
+    if (per_thread <= 2) launch(qk_norm_kv_store_vec_kernel<2>);
+    else if (per_thread <= 4) launch(qk_norm_kv_store_vec_kernel<4>);
+    else if (per_thread <= 8) launch(qk_norm_kv_store_vec_kernel<8>);
+    else launch(qk_norm_kv_store_vec_kernel<QKN_UNITS>);
     return tge_launched("qk_norm_kv_store_vec", 1);
   }
   if (is_bf16)

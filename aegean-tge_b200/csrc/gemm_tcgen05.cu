@@ -221,6 +221,36 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
       }
       continue;
     }
+    if (!p.to_partial && p.epilogue != GEMM_STORE_F32 && (p.ldo & 1) == 0 && ((uintptr_t)p.out & 3) == 0) {
+      // bfloat16 results, two weight rows to a store: neighbouring lanes exchange every other token column, the
+      // even lane then holds (row n, row n + 1) of the even columns and the odd lane those of the odd columns,
+      // so a lane issues eight 4-byte stores where it would issue sixteen of 2 bytes (the gated epilogue's way).
+      const bool odd = lane & 1;
+      const bool activate = p.epilogue >= GEMM_GELU && n >= p.act_from;
+      const int nn = odd ? n - 1 : n;
+#pragma unroll
+      for (int j = 0; j < 16; j += 2) {
+        float a = __uint_as_float(r[j]) + bias, b = __uint_as_float(r[j + 1]) + bias;
+        if (p.epilogue >= GEMM_GELU) {
+          if (activate) {
+            a = p.epilogue == GEMM_GELU ? gelu_erf_fast(a) : gelu_tanh(a);
+            b = p.epilogue == GEMM_GELU ? gelu_erf_fast(b) : gelu_tanh(b);
+          }
+        } else {
+          a *= p.alpha;
+          b *= p.alpha;
+        }
+        const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+        const float lo = odd ? got : a, hi = odd ? b : got;
+        const int m = m0 + j + (odd ? 1 : 0);
+        if (m < p.m_tok && nn < p.n_w) {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)m * p.ldo + nn;
+          if (nn + 1 < p.n_w) *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(lo, hi);
+          else *dst = __float2bfloat16_rn(lo);
+        }
+      }
+      continue;
+    }
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const int m = m0 + j;
@@ -1196,8 +1226,10 @@ __global__ void splitk_qkv_rope_store_kernel(const float* __restrict__ partial, 
 // them in float32, works out the two sums of squares, writes normalised q and k and (blended) v into the qkv
 // buffer and k and v into their pages; blocks y >= 1 add the partial sums of a slice of the up columns and write
 // their GELU.  One kernel where the separate path runs two sums of partial products and the norm-and-store.
-constexpr int QKV_ACT_THREADS = 512;
-constexpr int QKV_ACT_SLICE = 2048;              // up columns per block
+constexpr int QKV_ACT_THREADS = 1024;
+constexpr int QKV_PER_THREAD = 8;                // q, k and v columns per thread: up to 8,192 of them
+constexpr int ACT_PER_THREAD = 4;
+constexpr int QKV_ACT_SLICE = QKV_ACT_THREADS * ACT_PER_THREAD;      // up columns per block
 
 __global__ void __launch_bounds__(QKV_ACT_THREADS)
 splitk_qkv_norm_act_store_kernel(const float* __restrict__ partial, int m_tok, int n_w, int splits,
@@ -1209,29 +1241,40 @@ splitk_qkv_norm_act_store_kernel(const float* __restrict__ partial, int m_tok, i
                                  __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages, int num_pages,
                                  int page_size, int heads, int kv_heads, int head_dim, int value_dim, int store_kv,
                                  int* status, const float* __restrict__ ss, int ss_slices, int ss_width, float ss_eps) {
-  extern __shared__ float row_values[];
-  __shared__ float scratch[32];
+  __shared__ float scratch[64];
   pdl_trigger();
   const int t = blockIdx.x;
   const size_t plane = (size_t)m_tok * n_w;
   const int n_q = heads * head_dim, n_k = kv_heads * head_dim, n_v = kv_heads * value_dim;
   const int n_qkv = n_q + n_k + n_v;
   if (blockIdx.y > 0) {
+    // a slice of the up columns: every load of the partial sums is asked for before the first is used
     const int first = n_qkv + ((int)blockIdx.y - 1) * QKV_ACT_SLICE;
-    const int last = min(first + QKV_ACT_SLICE, n_w);
     pdl_wait();
-    const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, t);
-    for (int c = first + threadIdx.x; c < last; c += QKV_ACT_THREADS) {
-      const float* src = partial + (size_t)t * n_w + c;
-      float acc = 0.0f;
+    float acc[ACT_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < ACT_PER_THREAD; ++i) {
+      const int c = first + threadIdx.x + i * QKV_ACT_THREADS;
+      acc[i] = 0.0f;
+      if (c < n_w) {
+        const float* src = partial + (size_t)t * n_w + c;
 #pragma unroll 4
-      for (int s = 0; s < splits; ++s) acc += src[s * plane];
-      acc *= factor;
-      act_out[(size_t)t * ld_act + (c - n_qkv)] = __float2bfloat16_rn(activation == GEMM_GELU ? gelu_erf_fast(acc) : gelu_tanh(acc));
+        for (int s = 0; s < splits; ++s) acc[i] += src[s * plane];
+      }
+    }
+    const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, t);
+#pragma unroll
+    for (int i = 0; i < ACT_PER_THREAD; ++i) {
+      const int c = first + threadIdx.x + i * QKV_ACT_THREADS;
+      if (c < n_w) {
+        const float v = acc[i] * factor;
+        act_out[(size_t)t * ld_act + (c - n_qkv)] = __float2bfloat16_rn(activation == GEMM_GELU ? gelu_erf_fast(v) : gelu_tanh(v));
+      }
     }
     return;
   }
-  // what the step was given and the model's constants: read while the product still runs
+  // What the step was given and the model's constants are read while the product still runs: the position, the
+  // page, the blend's weight, the norm weights of this thread's columns.
   const int pos = positions[t];
   const float lambda = blend != nullptr ? blend[0] : 0.0f;
   int page = -1, slot = 0;
@@ -1241,21 +1284,47 @@ splitk_qkv_norm_act_store_kernel(const float* __restrict__ partial, int m_tok, i
     page = (pos >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
     slot = pos - page_index * page_size;
   }
+  float gain[QKV_PER_THREAD];
+#pragma unroll
+  for (int i = 0; i < QKV_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * QKV_ACT_THREADS;
+    gain[i] = 1.0f;
+    if (c < n_q) { if (q_weight != nullptr) gain[i] = q_weight[c]; }
+    else if (c < n_q + n_k) { if (k_weight != nullptr) gain[i] = k_weight[c - n_q]; }
+  }
   pdl_wait();
+  float value[QKV_PER_THREAD], other[QKV_PER_THREAD];
+#pragma unroll
+  for (int i = 0; i < QKV_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * QKV_ACT_THREADS;
+    value[i] = 0.0f;
+    other[i] = 0.0f;
+    if (c < n_qkv) {
+      const float* src = partial + (size_t)t * n_w + c;
+#pragma unroll 4
+      for (int s = 0; s < splits; ++s) value[i] += src[s * plane];
+      if (v_other != nullptr && c >= n_q + n_k) other[i] = __bfloat162float(v_other[(size_t)t * ld_other + (c - n_q - n_k)]);
+    }
+  }
   const float factor = row_factor_of(ss, ss_slices, ss_width, ss_eps, m_tok, t);
   float sum_q = 0.0f, sum_k = 0.0f;
-  for (int c = threadIdx.x; c < n_qkv; c += QKV_ACT_THREADS) {
-    const float* src = partial + (size_t)t * n_w + c;
-    float acc = 0.0f;
-#pragma unroll 4
-    for (int s = 0; s < splits; ++s) acc += src[s * plane];
-    acc *= factor;
-    row_values[c] = acc;
-    if (c < n_q) sum_q = fmaf(acc, acc, sum_q);
-    else if (c < n_q + n_k) sum_k = fmaf(acc, acc, sum_k);
+#pragma unroll
+  for (int i = 0; i < QKV_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * QKV_ACT_THREADS;
+    value[i] *= factor;
+    if (c < n_q) sum_q = fmaf(value[i], value[i], sum_q);
+    else if (c < n_q + n_k) sum_k = fmaf(value[i], value[i], sum_k);
   }
-  sum_q = block_sum(sum_q, scratch);
-  sum_k = block_sum(sum_k, scratch);
+  // both sums through one pair of barriers, in an order that depends on the block size alone
+  {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    sum_q = warp_sum(sum_q);
+    sum_k = warp_sum(sum_k);
+    if (lane == 0) { scratch[warp] = sum_q; scratch[32 + warp] = sum_k; }
+    __syncthreads();
+    sum_q = warp_sum(lane < QKV_ACT_THREADS / 32 ? scratch[lane] : 0.0f);
+    sum_k = warp_sum(lane < QKV_ACT_THREADS / 32 ? scratch[32 + lane] : 0.0f);
+  }
   const float f_q = q_weight != nullptr ? 1.0f / sqrtf(sum_q / (float)n_q + eps) : 1.0f;
   const float f_k = k_weight != nullptr ? 1.0f / sqrtf(sum_k / (float)n_k + eps) : 1.0f;
   bool store = store_kv != 0;
@@ -1264,25 +1333,27 @@ splitk_qkv_norm_act_store_kernel(const float* __restrict__ partial, int m_tok, i
     store = false;
   }
   __nv_bfloat16* row = qkv + (size_t)t * ld_qkv;
-  for (int c = threadIdx.x; c < n_qkv; c += QKV_ACT_THREADS) {       // each thread the columns it summed itself
-    float v = row_values[c];
+#pragma unroll
+  for (int i = 0; i < QKV_PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * QKV_ACT_THREADS;
+    if (c >= n_qkv) continue;
     if (c < n_q) {
-      row[c] = __float2bfloat16_rn(q_weight != nullptr ? v * f_q * q_weight[c] : v);
+      row[c] = __float2bfloat16_rn(q_weight != nullptr ? value[i] * f_q * gain[i] : value[i]);
     } else if (c < n_q + n_k) {
-      const int i = c - n_q;
-      const __nv_bfloat16 out = __float2bfloat16_rn(k_weight != nullptr ? v * f_k * k_weight[i] : v);
+      const int e = c - n_q;
+      const __nv_bfloat16 out = __float2bfloat16_rn(k_weight != nullptr ? value[i] * f_k * gain[i] : value[i]);
       row[c] = out;
       if (store) {
-        const int h = i / head_dim, d = i - h * head_dim;
+        const int h = e / head_dim, d = e - h * head_dim;
         k_pages[(((size_t)page * kv_heads + h) * page_size + slot) * head_dim + d] = out;
       }
     } else {
-      const int i = c - n_q - n_k;
-      if (v_other != nullptr) v = (1.0f - lambda) * v + lambda * __bfloat162float(v_other[(size_t)t * ld_other + i]);
+      const int e = c - n_q - n_k;
+      const float v = v_other != nullptr ? (1.0f - lambda) * value[i] + lambda * other[i] : value[i];
       const __nv_bfloat16 out = __float2bfloat16_rn(v);
       row[c] = out;
       if (store) {
-        const int h = i / value_dim, d = i - h * value_dim;
+        const int h = e / value_dim, d = e - h * value_dim;
         v_pages[(((size_t)page * kv_heads + h) * page_size + slot) * value_dim + d] = out;
       }
     }
@@ -1458,18 +1529,12 @@ TGE_API int tge_gemm_tcgen05_qkv_norm_act(const void* x, long long ldx, const vo
   TGE_REQUIRE(status != nullptr && (!store_kv || (page_size > 0 && max_pages > 0 && num_pages > 0)), "gemm+qk-norm: bad arguments");
   TGE_REQUIRE(eps > 0.0f || (q_weight == nullptr && k_weight == nullptr), "gemm+qk-norm: eps must be positive");
   if (M == 0) return 0;
-  if (M > FUSED_MAX_TOKENS || (size_t)n_qkv * sizeof(float) > 200 * 1024 || scratch == nullptr) return TGE_UNSUPPORTED;
+  if (M > FUSED_MAX_TOKENS || n_qkv > (long long)QKV_ACT_THREADS * QKV_PER_THREAD || scratch == nullptr) return TGE_UNSUPPORTED;
   int splits = 0;
   int rc = launch_product(x, ldx, w, ldw, nullptr, qkv, ld_qkv, M, N, K, GEMM_STORE, scratch, scratch_floats, 0, 0, true,
                           status, stream, &splits);
   if (rc != 1) return rc;
-  const size_t smem = (size_t)n_qkv * sizeof(float);
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t err = cudaFuncSetAttribute(splitk_qkv_norm_act_store_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    TGE_REQUIRE(err == cudaSuccess, "gemm+qk-norm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(err));
-    configured = smem;
-  }
+  const size_t smem = 0;
   const int act_blocks = (int)((N - n_qkv + QKV_ACT_SLICE - 1) / QKV_ACT_SLICE);
   tge_launch(splitk_qkv_norm_act_store_kernel, dim3(M, 1 + act_blocks), QKV_ACT_THREADS, smem, stream,
              (const float*)scratch, M, N, splits, (__nv_bfloat16*)qkv, ld_qkv, (__nv_bfloat16*)act_out, ld_act, activation,
