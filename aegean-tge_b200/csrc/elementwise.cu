@@ -559,8 +559,16 @@ __global__ void __launch_bounds__(QKN_THREADS) qk_norm_kv_store_vec_kernel(
     for (int e = 0; e < 8; ++e) part = fmaf(f[e], f[e], part);
     if (u < q_units) sum_q += part; else sum_k += part;
   }
-  sum_q = block_sum(sum_q, scratch);
-  sum_k = block_sum(sum_k, scratch);
+  {
+    // both sums through one pair of barriers, in an order that depends on the block size alone
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    sum_q = warp_sum(sum_q);
+    sum_k = warp_sum(sum_k);
+    if (lane == 0) { scratch[warp] = sum_q; scratch[QKN_THREADS / 32 + warp] = sum_k; }
+    __syncthreads();
+    sum_q = warp_sum(lane < QKN_THREADS / 32 ? scratch[lane] : 0.0f);
+    sum_k = warp_sum(lane < QKN_THREADS / 32 ? scratch[QKN_THREADS / 32 + lane] : 0.0f);
+  }
   const float f_q = 1.0f / sqrtf(sum_q / (float)(q_units * 8) + eps);
   const float f_k = 1.0f / sqrtf(sum_k / (float)(k_units * 8) + eps);
 #pragma unroll
