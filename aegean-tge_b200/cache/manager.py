@@ -1,9 +1,11 @@
 """Cache manager: paged per-token cache in groups, and fixed-size state slots.
 
-Layers whose mixers declare the same :class:`PagedCacheSpec` form a *group*.
-A group has its own page pool, and one page id of the group addresses the same
-page in every layer of the group, so a request has one block table per group,
-not per layer.  Groups with a window give pages back as soon as no later
+Layers whose mixers keep pages for the same positions (the same window, or none)
+form a *group*.  A group has its own page pool, and one page id of the group
+addresses the same page in every layer of the group, so a request has one block
+table per group, not per layer.  What a page holds may differ between the layers
+of a group (other head counts and sizes): layers with equal entries are stacked in
+one tensor per entry, a *variant* of the group.  Groups with a window give pages back as soon as no later
 query can read them.  Beside the pages, every live request owns one *state
 slot*: a row in each fixed-size state tensor that mixers with state declare
 (this architecture's attention declares none; the slot still exists and is
@@ -76,16 +78,26 @@ class PageGroup:
     page_size: int
     pool: PagePool
     tables: _Tables
-    storage: Dict[str, torch.Tensor] = field(default_factory=dict)      # name -> [layers, pages, ...]
+    # Layers of a group keep pages for the same positions (one block table, one pool), but what a page holds may
+    # differ from layer to layer (other head counts and sizes).  Layers whose entries are equal are stacked in one
+    # tensor per entry, a *variant*: (entries, its layers in order).
+    variants: List[Tuple[Tuple, List[int]]] = field(default_factory=list)
+    variant_storage: List[Dict[str, torch.Tensor]] = field(default_factory=list)   # per variant: name -> [layers, pages, ...]
+
+    @property
+    def storage(self) -> Dict[str, torch.Tensor]:
+        """The tensors of the group's first variant (all of them when every layer keeps the same entries)."""
+        return self.variant_storage[0] if self.variant_storage else {}
 
     def bytes_per_page(self, element_size: int) -> int:
         per_token = 0
-        for _, shape in self.spec.entries:
-            count = 1
-            for d in shape:
-                count *= d
-            per_token += count
-        return per_token * self.page_size * element_size * len(self.layers)
+        for entries, layers in self.variants:
+            for _, shape in entries:
+                count = 1
+                for d in shape:
+                    count *= d
+                per_token += count * len(layers)
+        return per_token * self.page_size * element_size
 
     def first_needed_page(self, computed_tokens: int) -> int:
         """Index of the first logical page a query at position >= computed_tokens can still read."""
@@ -105,7 +117,8 @@ class CacheManager:
         self._cache = self._lib.tge_rt_cache_create(int(page_size), int(max_requests))
         self.groups: List[PageGroup] = []
         self.layer_group: Dict[int, int] = {}                # layer id -> group index
-        self.layer_row: Dict[int, int] = {}                  # layer id -> row in the group's storage
+        self.layer_row: Dict[int, int] = {}                  # layer id -> row in its variant's storage
+        self.layer_variant: Dict[int, int] = {}              # layer id -> which variant of its group
         self.state_specs: Dict[int, StateSpec] = {}          # layer id -> its state
         self.state_storage: Dict[int, Dict[str, torch.Tensor]] = {}
         # request id <-> the runtime's handle; a mapping lives while the request is live here or pinned
@@ -154,21 +167,29 @@ class CacheManager:
 
     # -- construction ---------------------------------------------------------
     def add_layer(self, layer: int, cache: Optional[PagedCacheSpec], state: Optional[StateSpec]) -> None:
-        """Declares what one layer keeps.  Layers with equal paged specs share a group."""
+        """Declares what one layer keeps.  Layers with equal needs - pages for the same positions, that is the
+        same window - share a group (one pool, one block table per request); within it, layers whose entries
+        are equal share a variant (one stacked tensor per entry)."""
         if cache is not None:
             for index, group in enumerate(self.groups):
-                if group.spec.group_key() == cache.group_key():
-                    self.layer_group[layer] = index
-                    self.layer_row[layer] = len(group.layers)
-                    group.layers.append(layer)
+                if group.spec.window == cache.window:
                     break
             else:
                 index = _rt.check(self._lib.tge_rt_cache_add_group(self._cache, -1 if cache.window is None else int(cache.window)))
                 assert index == len(self.groups)
-                self.layer_group[layer] = index
-                self.layer_row[layer] = 0
                 pool = PagePool(_borrowed=self._lib.tge_rt_cache_pool(self._cache, index))
-                self.groups.append(PageGroup(cache, [layer], self.page_size, pool, _Tables(self, index)))
+                self.groups.append(PageGroup(cache, [], self.page_size, pool, _Tables(self, index)))
+                group = self.groups[index]
+            group.layers.append(layer)
+            self.layer_group[layer] = index
+            for number, (entries, layers) in enumerate(group.variants):
+                if entries == cache.entries:
+                    self.layer_variant[layer], self.layer_row[layer] = number, len(layers)
+                    layers.append(layer)
+                    break
+            else:
+                self.layer_variant[layer], self.layer_row[layer] = len(group.variants), 0
+                group.variants.append((cache.entries, [layer]))
         if state is not None:
             self.state_specs[layer] = state
 
@@ -211,10 +232,13 @@ class CacheManager:
         have one row more than there are slots (:attr:`scratch_slot`).
         """
         for group in self.groups:
-            group.storage = {}
-            for name, shape in group.spec.entries:
-                full = (len(group.layers), group.pool.capacity + 1, *shape[:-1], self.page_size, shape[-1])
-                group.storage[name] = torch.zeros(full, dtype=dtype, device=device)
+            group.variant_storage = []
+            for entries, layers in group.variants:
+                tensors = {}
+                for name, shape in entries:
+                    full = (len(layers), group.pool.capacity + 1, *shape[:-1], self.page_size, shape[-1])
+                    tensors[name] = torch.zeros(full, dtype=dtype, device=device)
+                group.variant_storage.append(tensors)
         self.state_storage = {}
         for layer, spec in self.state_specs.items():
             self.state_storage[layer] = {
@@ -230,7 +254,7 @@ class CacheManager:
             group = self.groups[group_index]
             row = self.layer_row[holder]
             cache.group = group_index
-            cache.paged = {name: tensor[row] for name, tensor in group.storage.items()}
+            cache.paged = {name: tensor[row] for name, tensor in group.variant_storage[self.layer_variant[holder]].items()}
             cache.owner = source is None
         if layer in self.state_storage:
             cache.state = self.state_storage[layer]

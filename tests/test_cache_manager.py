@@ -266,3 +266,30 @@ def test_a_padded_step_gets_idle_portions_on_the_scratch_page():
     m.check()
     with pytest.raises(ValueError, match="only a step of single tokens can be padded"):
         pack([Portion("a", [5, 6], [0]), Portion("b", [6], [0])], 4, 5)
+
+
+def test_layers_of_unlike_shapes_share_a_group_and_keep_storage_of_their_own():
+    """Ten layers, every one with another number of kv heads or other sizes for keys and values: one group (they all
+    keep every position), one block table, and page tensors per shape."""
+    from aegean_tge_b200.parts.base import PagedCacheSpec
+    shapes = [(1 + n % 4, 8 * (1 + n // 4), 4 * (1 + n % 3)) for n in range(10)]
+    shapes[7] = shapes[2]                                         # two layers alike: they are stacked
+    m = CacheManager(page_size=16, max_requests=4)
+    for layer, (kv, dim, vdim) in enumerate(shapes):
+        m.add_layer(layer, PagedCacheSpec(entries=(("k", (kv, dim)), ("v", (kv, vdim)))), None)
+    m.add_layer(10, PagedCacheSpec(entries=(("k", (2, 8)), ("v", (2, 8))), window=32), None)
+    assert len(m.groups) == 2 and m.groups[0].layers == list(range(10)) and m.groups[1].layers == [10]
+    assert len(m.groups[0].variants) == 9 and m.layer_variant[7] == m.layer_variant[2] and m.layer_row[7] == 1
+    m.set_pool_sizes([6, 6])
+    m.allocate_storage(torch.float32, torch.device("cpu"))
+    for layer, (kv, dim, vdim) in enumerate(shapes):
+        view = m.layer_cache(layer)
+        assert view.group == 0 and view.paged["k"].shape == (7, kv, 16, dim) and view.paged["v"].shape == (7, kv, 16, vdim)
+    assert m.layer_cache(7).paged["k"].data_ptr() != m.layer_cache(2).paged["k"].data_ptr()
+    per_token = sum(kv * (dim + vdim) for kv, dim, vdim in shapes)
+    assert m.groups[0].bytes_per_page(2) == per_token * 16 * 2
+    m.admit("a")
+    m.grow("a", 40)
+    assert m.groups[0].tables["a"] == [0, 1, 2] and len(m.groups[1].tables["a"]) == 3
+    m.free("a")
+    m.check()
