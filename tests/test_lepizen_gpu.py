@@ -191,6 +191,18 @@ def test_sink_attention_with_cut_keys_counts_the_sink_once(ops, heads, kv_heads,
     assert err < KERNEL_TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(6, 2, 48, 16), (8, 2, 64, 64), (4, 1, 128, 64)])
+@pytest.mark.parametrize("page_size,split", [(16, 0), (64, 128), (64, 64)])
+def test_single_tokens_at_the_head_of_a_mixed_step_keep_their_sinks(ops, heads, kv_heads, dim, vdim, page_size, split):
+    """Nine single tokens deep in their contexts beside two prompt portions: the single tokens go to the decode
+    kernel (their keys cut), the portions to the prompt kernel, both with the sink, one far key carrying a row."""
+    q_lens = [1] * 9 + [37, 70]
+    starts = [600, 0, 511, 512, 130, 64, 63, 1000, 257, 30, 200]
+    err, _, _ = _sink_attention_case(ops, torch.bfloat16, heads, kv_heads, dim, vdim, q_lens, starts, split=split,
+                                     page_size=page_size, sink_value=1.5, decode_prefix=9, spike=(0, 5, 0))
+    assert err < KERNEL_TOL[torch.bfloat16]
+
+
 @pytest.mark.parametrize("dtype,simt", [(torch.float32, True), (torch.bfloat16, True), (torch.bfloat16, False)])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(6, 2, 48, 16), (8, 2, 64, 64)])
 def test_a_sink_left_out_would_show(ops, dtype, simt, heads, kv_heads, dim, vdim):
@@ -534,3 +546,36 @@ def test_trace_replay_of_a_lepizen_model(folders, oracle, tmp_path, dtype):
     for step, ref in want.items():
         got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(ref.shape))
         assert rel_error(got, ref) < MODEL_TOL[dtype]
+
+
+def test_command_line_serves_the_design(folders, capsys):
+    """`tge generate`, `tge bench decode / prefill / mixed` and `tge plan` with a Lepizen folder: the commands know no design."""
+    from aegean_tge_b200.cli import main
+    assert main(["generate", "--model", folders["D"], "--tokens", "5 17 3", "--n", "6", "--print-ids", "--context", "128"]) == 0
+    out = capsys.readouterr().out
+    assert "prefill  :" in out and "decode   :" in out and len(out.split("ids      :")[1].split()) == 6
+    common = ["--model", folders["D"], "--context", "512", "--max-requests", "12"]
+    assert main(["bench", "decode", *common, "--batch", "3", "--prompt-len", "40", "--n", "4"]) == 0
+    assert main(["bench", "prefill", *common, "--prompt-len", "100", "--repeat", "1"]) == 0
+    assert main(["bench", "mixed", *common, "--batch", "9", "--prompt-len", "40", "--portion", "70", "--timeline"]) == 0
+    out = capsys.readouterr().out
+    assert "decode   : batch 3 at context 40" in out and "attention_decode" in out
+    assert main(["plan", "--model", folders["A"], "--context", "256", "--sessions", "2"]) == 0
+    assert "kv       :" in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampled_generation_with_requests_that_come_and_go(folders, dtype):
+    """Twelve requests with temperature, top-k and top-p samplers through six slots and a small pool: all finish,
+    the same seeds give the same tokens whatever shared a step with what, every page comes back."""
+    from aegean_tge_b200 import SamplingParams
+    prompts = [_tokens("A", 3 + 11 * i, salt=300 + i) for i in range(12)]
+    params = [SamplingParams(temperature=0.8, top_k=(0, 20, 50)[i % 3], top_p=(1.0, 0.9)[i % 2], seed=40 + i) for i in range(12)]
+    outputs = []
+    for slots, budget, chunk in ((6, 64, 16), (3, 256, 64)):
+        engine = _engine(folders, "A", dtype, max_requests=slots, max_batch_tokens=budget, chunk=chunk, max_tokens=640)
+        outputs.append(engine.generate(prompts, n=10, sampling=params))
+        assert all(len(row) == 10 for row in outputs[-1]) and not engine.cache.live_requests()
+        engine.cache.check()
+    if dtype == "float32":
+        assert outputs[0] == outputs[1]
