@@ -725,7 +725,10 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         out = torch.empty((tokens, heads * value_dim), dtype=q.dtype, device=q.device)
     _want(out, "attention output", q.dtype, contiguous=False)
     out_stride = _rows_2d(out, "attention output")
-    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt
+    # the tensor-core kernels read and write pairs of bfloat16: rows that start on odd elements (an inner buffer
+    # whose neighbour has an odd width, say) go to the CUDA-core kernel
+    pairs_ok = (q_stride % 2 == 0 and out_stride % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
                and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim))
     if use_mma:
         lib = attention_lib(head_dim, value_dim)

@@ -2,7 +2,7 @@
 
 First every mechanism alone through its kernel (sink attention with values of their own size, the projection norm
 with value blend and cache store, the GELU and scaled-add product epilogues, the soft cap), with inputs made so
-that a lost sink, a far key or a blend left out shows; then whole models of five small configurations that differ
+that a lost sink, a far key or a blend left out shows; then whole models of six small configurations that differ
 in every size and option, cut and batched in every way, both number formats.
 """
 import copy
@@ -50,8 +50,11 @@ CONFIGS = {
     "D": _config(300, 128, 1e-6, 0.4, 9.0, 12.0, [_layer(8, 2, 64, 64, 0.125, True, 192), _layer(8, 2, 64, 64, 0.125, True, 192)]),
     # keys of 128 and values of 64, four query heads on one kv head
     "E": _config(160, 128, 1e-6, 0.6, 5.0, 15.0, [_layer(4, 1, 128, 64, 0.09, True, 256), _layer(8, 1, 48, 64, 0.14, True, 64)]),
+    # tensor-core head sizes beside an odd inner width and an odd vocabulary: the buffer that the attention and the
+    # feed-forward share then has rows of an odd length
+    "F": _config(131, 96, 1e-6, 0.7, 3.0, 25.0, [_layer(4, 2, 32, 16, 0.2, True, 77), _layer(2, 1, 16, 48, 0.3, False, 51)]),
 }
-SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14, "E": 15}
+SEEDS = {"A": 11, "B": 12, "C": 13, "D": 14, "E": 15, "F": 16}
 
 
 @pytest.fixture(scope="module")
