@@ -220,8 +220,8 @@ def paired_configs(width: int, heads: int, kv_heads: int, head_dim: int, gated_i
              "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
                        "v_mix": True},
              "mlp": {"kind": "dense", "ff": gated_inner * 3 // 2}}
-    lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.3,
-               "logit_scale": 2.0, "logit_softcap": 30.0, "layers": [layer] * layers}
+    lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+               "logit_scale": 1.0, "logit_softcap": 50.0, "layers": [layer] * layers}
     return {"qwen2": qwen2, "lepizen": lepizen}
 
 
