@@ -119,6 +119,7 @@ class CacheManager:
         self.layer_group: Dict[int, int] = {}                # layer id -> group index
         self.layer_row: Dict[int, int] = {}                  # layer id -> row in its variant's storage
         self.layer_variant: Dict[int, int] = {}              # layer id -> which variant of its group
+        self.layer_extras: Dict[int, List[str]] = {}         # layer id -> names of its further paged caches
         self.state_specs: Dict[int, StateSpec] = {}          # layer id -> its state
         self.state_storage: Dict[int, Dict[str, torch.Tensor]] = {}
         # request id <-> the runtime's handle; a mapping lives while the request is live here or pinned
@@ -166,32 +167,45 @@ class CacheManager:
         self._names.pop(self._handles.pop(request), None)
 
     # -- construction ---------------------------------------------------------
-    def add_layer(self, layer: int, cache: Optional[PagedCacheSpec], state: Optional[StateSpec]) -> None:
+    def add_layer(self, layer: int, cache: Optional[PagedCacheSpec], state: Optional[StateSpec],
+                  extra: Optional[Dict[str, PagedCacheSpec]] = None) -> None:
         """Declares what one layer keeps.  Layers with equal needs - pages for the same positions, that is the
-        same window - share a group (one pool, one block table per request); within it, layers whose entries
-        are equal share a variant (one stacked tensor per entry)."""
+        same window and the same positions per entry - share a group (one pool, one block table per request);
+        within it, layers whose entries are equal share a variant (one stacked tensor per entry).  ``extra``:
+        further paged caches of the layer by name (pooled entries, one per block of positions), each placed in a
+        group the same way."""
         if cache is not None:
-            for index, group in enumerate(self.groups):
-                if group.spec.window == cache.window:
-                    break
-            else:
-                index = _rt.check(self._lib.tge_rt_cache_add_group(self._cache, -1 if cache.window is None else int(cache.window)))
-                assert index == len(self.groups)
-                pool = PagePool(_borrowed=self._lib.tge_rt_cache_pool(self._cache, index))
-                self.groups.append(PageGroup(cache, [], self.page_size, pool, _Tables(self, index)))
-                group = self.groups[index]
-            group.layers.append(layer)
-            self.layer_group[layer] = index
-            for number, (entries, layers) in enumerate(group.variants):
-                if entries == cache.entries:
-                    self.layer_variant[layer], self.layer_row[layer] = number, len(layers)
-                    layers.append(layer)
-                    break
-            else:
-                self.layer_variant[layer], self.layer_row[layer] = len(group.variants), 0
-                group.variants.append((cache.entries, [layer]))
+            self._add_paged(layer, cache)
+        for name, spec in (extra or {}).items():
+            self._add_paged((layer, name), spec)
+            self.layer_extras.setdefault(layer, []).append(name)
         if state is not None:
             self.state_specs[layer] = state
+
+    def _add_paged(self, layer, cache: PagedCacheSpec) -> None:
+        for index, group in enumerate(self.groups):
+            if group.spec.window == cache.window and group.spec.stride == cache.stride:
+                break
+        else:
+            window = -1 if cache.window is None else int(cache.window)
+            if cache.stride == 1:
+                index = _rt.check(self._lib.tge_rt_cache_add_group(self._cache, window))
+            else:
+                index = _rt.check(self._lib.tge_rt_cache_add_group_strided(self._cache, window, int(cache.stride)))
+            assert index == len(self.groups)
+            pool = PagePool(_borrowed=self._lib.tge_rt_cache_pool(self._cache, index))
+            self.groups.append(PageGroup(cache, [], self.page_size, pool, _Tables(self, index)))
+            group = self.groups[index]
+        group.layers.append(layer)
+        self.layer_group[layer] = index
+        for number, (entries, layers) in enumerate(group.variants):
+            if entries == cache.entries:
+                self.layer_variant[layer], self.layer_row[layer] = number, len(layers)
+                layers.append(layer)
+                break
+        else:
+            self.layer_variant[layer], self.layer_row[layer] = len(group.variants), 0
+            group.variants.append((cache.entries, [layer]))
 
     def set_pool_sizes(self, pages_per_group: Sequence[int]) -> None:
         if len(pages_per_group) != len(self.groups):
@@ -213,16 +227,19 @@ class CacheManager:
         if not self.groups:
             return []
         if tokens is not None:
-            pages = max(-(-tokens // self.page_size), 1)
-            return [pages] * len(self.groups)
+            # a group of pooled entries holds one per ``stride`` positions, and a page of every live request may
+            # be partly filled
+            return [max(-(-tokens // self.page_size), 1) if g.spec.stride == 1 else
+                    max(-(-tokens // (self.page_size * g.spec.stride)) + self.max_requests, 1) for g in self.groups]
         if budget_bytes is None:
             raise ValueError("cache manager: give tokens or budget_bytes")
-        per_page = sum(g.bytes_per_page(element_size) for g in self.groups)
-        pages = budget_bytes // per_page
+        per_page = sum(g.bytes_per_page(element_size) / g.spec.stride for g in self.groups)
+        pages = int(budget_bytes // per_page)
         if pages < 1:
             raise PoolExhausted(f"cache manager: {budget_bytes} bytes do not hold one page of every group "
                                 f"({per_page} bytes)")
-        return [int(pages)] * len(self.groups)
+        return [int(pages) if g.spec.stride == 1 else max(int(pages) // g.spec.stride + self.max_requests, 1)
+                for g in self.groups]
 
     def allocate_storage(self, dtype: torch.dtype, device: torch.device) -> None:
         """Creates the page and state tensors (zero-filled, so stale pages hold finite values).
@@ -256,6 +273,13 @@ class CacheManager:
             cache.group = group_index
             cache.paged = {name: tensor[row] for name, tensor in group.variant_storage[self.layer_variant[holder]].items()}
             cache.owner = source is None
+        for name in self.layer_extras.get(holder, []):
+            key = (holder, name)
+            more = LayerCache(group=self.layer_group[key], owner=source is None)
+            group = self.groups[more.group]
+            more.paged = {entry: tensor[self.layer_row[key]]
+                          for entry, tensor in group.variant_storage[self.layer_variant[key]].items()}
+            cache.more[name] = more
         if layer in self.state_storage:
             cache.state = self.state_storage[layer]
         return cache

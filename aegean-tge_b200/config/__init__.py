@@ -5,6 +5,9 @@ from .common import ConfigError, read_config_json
 from .qwen2 import Qwen2Config
 from .lepizen import ARCHITECTURE as LEPIZEN_ARCHITECTURE
 from .lepizen import LepizenConfig
+from .mozepel import ARCHITECTURE as MOZEPEL_ARCHITECTURE
+from .mozepel import MozepelConfig
 
 __all__ = ["LayerSpec", "ModelSpec", "PartSpec", "expected_tensors", "ConfigError",
-           "Qwen2Config", "QWEN2_ARCHITECTURE", "LepizenConfig", "LEPIZEN_ARCHITECTURE", "read_config_json"]
+           "Qwen2Config", "QWEN2_ARCHITECTURE", "LepizenConfig", "LEPIZEN_ARCHITECTURE", "MozepelConfig", "MOZEPEL_ARCHITECTURE",
+           "read_config_json"]

@@ -36,6 +36,9 @@ class LayerSpec:
     ``feed_forward`` is None for a layer that has only a mixer, ``ffn_norm`` is
     None for an arrangement with one norm (both sublayers read its output);
     ``block_params`` are the arrangement's own constants (a residual multiplier).
+    ``weights_from`` names an earlier layer whose parts this layer runs (the same
+    tensors, loaded once), with a cache and state of its own; its part specs
+    then equal that layer's.
     """
 
     block: str
@@ -45,6 +48,7 @@ class LayerSpec:
     ffn_norm: Optional[PartSpec]
     cache_from: Optional[int] = None
     block_params: Mapping[str, Any] = field(default_factory=dict)
+    weights_from: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -77,6 +81,15 @@ class ModelSpec:
             if not 0 <= index < len(self.layers):
                 raise ValueError(f"model spec: schedule[{step}]={index} names no layer")
         for index, layer in enumerate(self.layers):
+            if layer.weights_from is not None:
+                source = layer.weights_from
+                if not 0 <= source < index or self.layers[source].weights_from is not None:
+                    raise ValueError(f"model spec: layer {index} runs the parts of layer {source}, which must be an "
+                                     f"earlier layer with parts of its own")
+                other = self.layers[source]
+                if (other.block, other.mixer, other.feed_forward, other.mixer_norm, other.ffn_norm, dict(other.block_params)) != \
+                        (layer.block, layer.mixer, layer.feed_forward, layer.mixer_norm, layer.ffn_norm, dict(layer.block_params)):
+                    raise ValueError(f"model spec: layer {index} runs the parts of layer {source} but is described differently")
             if layer.cache_from is not None:
                 if not 0 <= layer.cache_from < len(self.layers) or layer.cache_from == index:
                     raise ValueError(f"model spec: layer {index} reads the cache of layer "

@@ -12,6 +12,9 @@
 // The causal mask is the loop bound; `window` > 0 additionally drops keys older
 // than p - window + 1.  Values may have a size of their own (`value_dim`), and a head may have a sink: a learned
 // score `sink[h]` that joins the softmax's denominator once, unscaled, with no key and no value behind it.
+// With a window and `pool` > 0 the query also sees, in the same softmax, one pooled key and value for every
+// block of `pool` positions that lies wholly before its window (block b if b*pool + pool - 1 <= p - window); they
+// are read from pages of their own, entry b where position b would be, and visited before the tokens.
 #include "common.cuh"
 
 namespace {
@@ -24,7 +27,8 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
     const int* __restrict__ block_table, int max_pages, int num_pages, int page_size,
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, T* __restrict__ out, int out_stride,
     int heads, int kv_heads, int head_dim, int value_dim, const float* __restrict__ sink, float scale, int window,
-    int* status) {
+    int pool, const T* __restrict__ kp_pages, const T* __restrict__ vp_pages, const int* __restrict__ pool_table,
+    int pool_max_pages, int pool_num_pages, int* status) {
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * 4 + warp;
@@ -45,6 +49,38 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
   }
   float m = -INFINITY, l = 0.0f;
   const int first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (pool > 0 && window > 0) {
+    const int seen = first / pool;                       // blocks that end at or before pos - window
+    const int* ptable = pool_table + (size_t)seq * pool_max_pages;
+    for (int entry = 0; entry < seen; ++entry) {
+      const int page_index = entry / page_size;
+      const int page = page_index < pool_max_pages ? ptable[page_index] : -1;
+      if (page < 0 || page >= pool_num_pages) {
+        if (lane == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+        break;
+      }
+      const T* krow = kp_pages + (((size_t)page * kv_heads + kvh) * page_size + entry % page_size) * head_dim;
+      const T* vrow = vp_pages + (((size_t)page * kv_heads + kvh) * page_size + entry % page_size) * value_dim;
+      float dot = 0.0f;
+#pragma unroll
+      for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < head_dim) dot = fmaf(qv[i], to_float<T>(krow[d]), dot);
+      }
+      dot = warp_sum(dot);
+      const float s = dot * scale;
+      const float m_new = fmaxf(m, s);
+      const float corr = expf(m - m_new);
+      const float p = expf(s - m_new);
+      l = l * corr + p;
+#pragma unroll
+      for (int i = 0; i < MAX_PER_LANE; ++i) {
+        const int d = lane + 32 * i;
+        if (d < value_dim) acc[i] = fmaf(p, to_float<T>(vrow[d]), acc[i] * corr);
+      }
+      m = m_new;
+    }
+  }
   for (int page_index = first / page_size; page_index * page_size <= pos; ++page_index) {
     const int page = page_index < max_pages ? table[page_index] : -1;
     if (page < 0 || page >= num_pages) {
@@ -102,7 +138,9 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
                                const int* block_table, int max_pages, int num_pages, int page_size,
                                const int* positions, const int* seq_of_token, void* out, int out_stride, int tokens,
                                int heads, int kv_heads, int head_dim, int value_dim, const float* sink, float scale,
-                               int window, int is_bf16, int* status, cudaStream_t stream) {
+                               int window, int is_bf16, int pool, const void* kp_pages, const void* vp_pages,
+                               const int* pool_table, int pool_max_pages, int pool_num_pages, int* status,
+                               cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
   TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE, "attention: head_dim %d outside (0, %d]", head_dim,
@@ -111,17 +149,21 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
               32 * MAX_PER_LANE);
   TGE_REQUIRE(page_size > 0 && max_pages > 0 && num_pages > 0, "attention: bad page geometry");
   TGE_REQUIRE(window >= 0, "attention: negative window");
+  TGE_REQUIRE(pool >= 0 && (pool == 0 || (window > 0 && kp_pages != nullptr && vp_pages != nullptr && pool_table != nullptr &&
+                                          pool_max_pages > 0 && pool_num_pages > 0)),
+              "attention: pooled blocks need a window, their pages and their table");
   if (tokens == 0) return 0;
   dim3 grid(tokens, (heads + 3) / 4);
   if (is_bf16)
     attention_simt_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
         max_pages, num_pages, page_size, positions, seq_of_token, (__nv_bfloat16*)out, out_stride, heads, kv_heads,
-        head_dim, value_dim, sink, scale, window, status);
+        head_dim, value_dim, sink, scale, window, pool, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages,
+        pool_table, pool_max_pages, pool_num_pages, status);
   else
     attention_simt_kernel<float><<<grid, 128, 0, stream>>>(
         (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_pages, num_pages,
         page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, sink, scale,
-        window, status);
+        window, pool, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, status);
   return tge_launched("attention_simt", 1);
 }

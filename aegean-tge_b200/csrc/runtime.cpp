@@ -96,6 +96,7 @@ struct TgeRtPool {
 struct TgeRtCache {
   struct Group {
     int window;                                              // < 0: none
+    int stride = 1;                                          // positions per entry: a group of pooled entries keeps one per block
     std::unique_ptr<TgeRtPool> pool;
     std::unordered_map<int64_t, std::vector<int>> tables;    // request -> logical page -> physical id
   };
@@ -112,7 +113,8 @@ struct TgeRtCache {
   TgeRtCache(int page, int requests) : page_size(page), max_requests(requests) {
     for (int slot = requests - 1; slot >= 0; --slot) free_slots.push_back(slot);
   }
-  int pages_for(int tokens) const { return (tokens + page_size - 1) / page_size; }
+  // Pages that cover `tokens` positions: of a strided group, the whole blocks among them.
+  int pages_for(const Group& group, int tokens) const { return (tokens / group.stride + page_size - 1) / page_size; }
   const Live* find(int64_t request) const {
     auto it = live.find(request);
     return it == live.end() ? nullptr : &it->second;
@@ -120,12 +122,12 @@ struct TgeRtCache {
   int first_needed_page(const Group& group, int computed_tokens) const {
     if (group.window < 0) return 0;
     const int first_key = std::max(computed_tokens - group.window + 1, 0);
-    return first_key / page_size;
+    return first_key / group.stride / page_size;
   }
   int missing(const Group& group, int64_t request, int total_tokens) const {
     auto it = group.tables.find(request);
     const int have = it == group.tables.end() ? 0 : (int)it->second.size();
-    return std::max(pages_for(total_tokens) - have, 0);
+    return std::max(pages_for(group, total_tokens) - have, 0);
   }
   bool can_grow(int64_t request, int total_tokens) const {
     for (const Group& group : groups)
@@ -134,7 +136,7 @@ struct TgeRtCache {
   }
   bool fits_empty_pool(int total_tokens) const {
     for (const Group& group : groups)
-      if (pages_for(total_tokens) > group.pool->capacity()) return false;
+      if (pages_for(group, total_tokens) > group.pool->capacity()) return false;
     return true;
   }
   int admit(int64_t request) {
@@ -464,9 +466,8 @@ struct TgeRtScheduler {
            !cache->free_slots.empty()) {
       Request* r = waiting.front();
       const int count = portion_size(r, budget);
-      const int pages = cache->pages_for(count);
       bool fits = true;
-      for (const auto& group : cache->groups) fits = fits && pages <= group.pool->free_count();
+      for (const auto& group : cache->groups) fits = fits && cache->pages_for(group, count) <= group.pool->free_count();
       if (!fits) break;
       waiting.pop_front();
       if (int rc = cache->admit(r->id); rc < 0) return rc;
@@ -551,10 +552,13 @@ TgeRtCache* tge_rt_cache_create(int page_size, int max_requests) {
   return new TgeRtCache(page_size, max_requests);
 }
 void tge_rt_cache_destroy(TgeRtCache* cache) { delete cache; }
-int tge_rt_cache_add_group(TgeRtCache* cache, int window) {
+int tge_rt_cache_add_group(TgeRtCache* cache, int window) { return tge_rt_cache_add_group_strided(cache, window, 1); }
+int tge_rt_cache_add_group_strided(TgeRtCache* cache, int window, int stride) {
   if (cache->groups.size() >= 8) return fail(TGE_RT_VALUE_ERROR, "cache manager: at most 8 groups");
   TgeRtCache::Group group;
+  if (stride <= 0) return fail(TGE_RT_VALUE_ERROR, "cache manager: a group keeps one entry per %d positions", stride);
   group.window = window;
+  group.stride = stride;
   group.pool.reset(new TgeRtPool(1));
   cache->groups.push_back(std::move(group));
   return (int)cache->groups.size() - 1;

@@ -40,6 +40,8 @@ typedef struct TgeRtCache TgeRtCache;
 TgeRtCache* tge_rt_cache_create(int page_size, int max_requests);
 void tge_rt_cache_destroy(TgeRtCache* cache);
 int tge_rt_cache_add_group(TgeRtCache* cache, int window);            // window < 0: every key is kept; returns the group's index
+// A group that keeps one entry per `stride` positions (the whole blocks among a request's tokens): pooled keys and values.
+int tge_rt_cache_add_group_strided(TgeRtCache* cache, int window, int stride);
 int tge_rt_cache_set_pool_size(TgeRtCache* cache, int group, int num_pages);
 TgeRtPool* tge_rt_cache_pool(TgeRtCache* cache, int group);          // owned by the cache
 int tge_rt_cache_groups(const TgeRtCache* cache);

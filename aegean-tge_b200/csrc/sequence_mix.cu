@@ -1,0 +1,508 @@
+// Kernels of the mixers that carry a fixed-size state from token to token, and of the layers around them:
+//
+//  * decay_scan       - linear attention with a fixed decay per head: S_t = c S_(t-1) + k_t v_t^T, o_t = S_t^T q_t,
+//                       the state in float32 in a per-request slot, q and k activated, rotated and scaled on the way in;
+//  * gated_norm       - RMS norm over groups of a row (a head, or all heads together), times an activated gate;
+//  * conv_norm_rope_store / conv_state_update - a short causal convolution over time on every channel of q, k and v
+//                       (its last taps-1 inputs kept per request), the per-head norm of q and k, their rotation, and
+//                       the store of k and v into their pages;
+//  * pool_kv          - the mean key and mean value of every block of P positions that a step completes;
+//  * scale_add_norm   - the layer that normalises after the sum: x <- rms(a x + y) g;
+//  * to_run_dtype     - float32 rows in the format the products read.
+//
+// All statistics, states, angles and sums are float32 in both number formats; what is bfloat16 in the
+// bfloat16 path is the projections these kernels read and the rows they hand to the next product.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void to_run_dtype_kernel(const float* __restrict__ x, T* __restrict__ out, size_t count) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = from_float<T>(x[i]);
+}
+
+// x[r, :] <- rms(alpha x[r, :] + y[r, :]) * weight, in place; `copy` (may be null) receives the same row in T.
+template <typename T>
+__global__ void __launch_bounds__(256) scale_add_norm_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                             long long ldy, const float* __restrict__ weight,
+                                                             T* __restrict__ copy, int hidden, float alpha, float eps) {
+  __shared__ float scratch[32];
+  float* row = x + (size_t)blockIdx.x * hidden;
+  const float* add = y + (size_t)blockIdx.x * ldy;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = fmaf(alpha, row[i], add[i]);
+    sum = fmaf(v, v, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = fmaf(alpha, row[i], add[i]) * scale * weight[i];
+    row[i] = v;
+    if (copy != nullptr) copy[(size_t)blockIdx.x * hidden + i] = from_float<T>(v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Linear attention with a decay per head.  A block owns 32 columns of one head's state for one request and walks
+// the request's tokens of this step in order, SCAN_TOKENS at a time: the block prepares their q and k (activation,
+// rotation, scale) in shared memory, every thread then updates its rows of its column token by token and adds up
+// its share of o, and the four row groups' shares are summed in a fixed order.  Columns of the state do not
+// interact, so the grid is (column tiles, heads, requests) and a result depends on nothing but the request's own
+// tokens in their order.
+constexpr int SCAN_TOKENS = 8;
+constexpr int SCAN_WARPS = 4;
+
+template <typename T, int ROWS>
+__global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
+    const T* __restrict__ rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
+    int activation, const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+    int rotary, float k_scale, const float* __restrict__ decay, float* __restrict__ state,
+    const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
+    float* __restrict__ out, int* status) {
+  extern __shared__ float shared[];
+  float* qs = shared;                                   // [SCAN_TOKENS][dim]
+  float* ks = qs + SCAN_TOKENS * dim;                   // [SCAN_TOKENS][dim]
+  float* partial = ks + SCAN_TOKENS * dim;              // [SCAN_WARPS][SCAN_TOKENS][32]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int column = blockIdx.x * 32 + lane;
+  const bool live = column < vdim;
+  const int first = q_start[seq], last = q_start[seq + 1];
+  if (first >= last) return;
+  const int slot = slots[seq];
+  const float c = decay[head];
+  const int half = rotary >> 1;
+  float* mine = state + (((size_t)slot * heads + head) * dim) * vdim + column;
+  float s[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int i = warp * ROWS + r;
+    s[r] = (live && i < dim) ? mine[(size_t)i * vdim] : 0.0f;
+  }
+  for (int base = first; base < last; base += SCAN_TOKENS) {
+    const int count = min(SCAN_TOKENS, last - base);
+    // q and k of these tokens as the recurrence takes them
+    for (int e = threadIdx.x; e < count * dim; e += blockDim.x) {
+      const int n = e / dim, i = e - n * dim;
+      const T* row = rows + (size_t)(base + n) * ld;
+      float q = to_float<T>(row[q_off + head * dim + i]);
+      float k = to_float<T>(row[k_off + head * dim + i]);
+      if (activation) { q = silu_f(q); k = silu_f(k); }
+      if (i < rotary) {
+        const int other = i < half ? i + half : i - half;
+        float q2 = to_float<T>(row[q_off + head * dim + other]);
+        float k2 = to_float<T>(row[k_off + head * dim + other]);
+        if (activation) { q2 = silu_f(q2); k2 = silu_f(k2); }
+        int position = positions[base + n];
+        if (position < 0 || position >= table_positions) {
+          atomicOr(status, TGE_STATUS_BAD_ROW);
+          position = 0;
+        }
+        const float cs = cos_table[(size_t)position * half + (i < half ? i : i - half)];
+        const float sn = sin_table[(size_t)position * half + (i < half ? i : i - half)];
+        // the pair (u, v) = (element i, element i + half) becomes (u cos - v sin, v cos + u sin)
+        q = i < half ? q * cs - q2 * sn : q * cs + q2 * sn;
+        k = i < half ? k * cs - k2 * sn : k * cs + k2 * sn;
+      }
+      qs[e] = q;
+      ks[e] = k * k_scale;
+    }
+    float v[SCAN_TOKENS];
+#pragma unroll
+    for (int n = 0; n < SCAN_TOKENS; ++n) {
+      float value = 0.0f;
+      if (live && n < count) {
+        value = to_float<T>(rows[(size_t)(base + n) * ld + v_off + head * vdim + column]);
+        if (activation) value = silu_f(value);
+      }
+      v[n] = value;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < SCAN_TOKENS; ++n) {
+      float acc = 0.0f;
+      if (n < count) {
+        const float* qn = qs + n * dim + warp * ROWS;
+        const float* kn = ks + n * dim + warp * ROWS;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          if (warp * ROWS + r < dim) {
+            s[r] = fmaf(kn[r], v[n], c * s[r]);
+            acc = fmaf(s[r], qn[r], acc);
+          }
+        }
+      }
+      partial[(warp * SCAN_TOKENS + n) * 32 + lane] = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < count * 32; e += blockDim.x) {
+      const int n = e >> 5, l = e & 31;
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < SCAN_WARPS; ++w) total += partial[(w * SCAN_TOKENS + n) * 32 + l];
+      const int col = blockIdx.x * 32 + l;
+      if (col < vdim) out[(size_t)(base + n) * heads * vdim + head * vdim + col] = total;
+    }
+    // the next round writes qs/ks before its first barrier, and partial after it: a barrier here keeps the
+    // sums above apart from both
+    __syncthreads();
+  }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const int i = warp * ROWS + r;
+    if (live && i < dim) mine[(size_t)i * vdim] = s[r];
+  }
+}
+
+// out[t, g*size + e] = o[t, g*size + e] / rms_g(o[t]) * weight[g*size + e] * act(gate[t, g*size + e]); one warp per
+// (token, group).  weight may be null (no weight); act 0: silu, 1: sigmoid.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate,
+                                                         long long ld_gate, const float* __restrict__ weight,
+                                                         T* __restrict__ out, long long ld_out, int tokens, int groups,
+                                                         int size, float eps, int act) {
+  const int lane = threadIdx.x & 31;
+  const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (unit >= (long long)tokens * groups) return;
+  const int t = (int)(unit / groups), g = (int)(unit - (long long)t * groups);
+  const float* src = o + ((size_t)t * groups + g) * size;
+  float sum = 0.0f;
+  for (int e = lane; e < size; e += 32) sum = fmaf(src[e], src[e], sum);
+  sum = warp_sum(sum);
+  const float scale = 1.0f / sqrtf(sum / (float)size + eps);
+  const T* gt = gate + (size_t)t * ld_gate + (size_t)g * size;
+  T* dst = out + (size_t)t * ld_out + (size_t)g * size;
+  for (int e = lane; e < size; e += 32) {
+    const float z = to_float<T>(gt[e]);
+    const float w = weight != nullptr ? weight[(size_t)g * size + e] : 1.0f;
+    dst[e] = from_float<T>(src[e] * scale * w * (act == 0 ? silu_f(z) : sigmoid_f(z)));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// After the q/k/v product: the short convolution over time, the per-head norm of q and k, their rotation, and the
+// store.  One warp per (token, head of q, k or v).  `raw` holds the projections of this step's tokens [T, q | k | v];
+// inputs from before the portion come from the request's convolution state [slots, taps-1, channels] (oldest first),
+// which is zero for a request that starts.  q goes to `q_out`, k and v into their pages.
+constexpr int CNR_PER_LANE = 8;    // head sizes up to 256
+constexpr int MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128) conv_norm_rope_store_kernel(
+    const T* __restrict__ raw, long long ld, const float* __restrict__ conv_w, int taps,
+    const float* __restrict__ conv_state, const int* __restrict__ slots, const int* __restrict__ q_start,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions, int rotary,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+    int max_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int page_size,
+    T* __restrict__ q_out, long long ld_q, int heads, int kv_heads, int dim, int vdim, int store, int* status) {
+  __shared__ float staged[4][32 * CNR_PER_LANE];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.y * 4 + warp;
+  if (unit >= heads + 2 * kv_heads) return;
+  const int kind = unit < heads ? 0 : (unit < heads + kv_heads ? 1 : 2);        // q, k, v
+  const int head = kind == 0 ? unit : (kind == 1 ? unit - heads : unit - heads - kv_heads);
+  const int size = kind == 2 ? vdim : dim;
+  const int channels = (heads + kv_heads) * dim + kv_heads * vdim;
+  const int channel0 = kind == 0 ? head * dim : (kind == 1 ? (heads + head) * dim : (heads + kv_heads) * dim + head * vdim);
+  const int seq = seq_of_token[t];
+  const int local = t - q_start[seq];                     // this token's index in its portion
+  const int slot = slots[seq];
+  float y[CNR_PER_LANE];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < CNR_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    float value = 0.0f;
+    if (e < size) {
+      const int c = channel0 + e;
+      if (taps <= 0) {
+        value = to_float<T>(raw[(size_t)t * ld + c]);
+      } else {
+        for (int j = 0; j < taps; ++j) {
+          const int back = taps - 1 - j;                  // how many tokens before this one
+          float u;
+          if (local - back >= 0) u = to_float<T>(raw[(size_t)(t - back) * ld + c]);
+          else u = conv_state[((size_t)slot * (taps - 1) + (taps - 1 + local - back)) * channels + c];
+          value = fmaf(conv_w[(size_t)c * taps + j], u, value);
+        }
+      }
+    }
+    y[i] = value;
+    sum = fmaf(value, value, sum);
+  }
+  const float* norm_w = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
+  if (norm_w != nullptr) {
+    sum = warp_sum(sum);
+    const float scale = 1.0f / sqrtf(sum / (float)size + eps);
+#pragma unroll
+    for (int i = 0; i < CNR_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < size) y[i] = y[i] * scale * norm_w[e];
+    }
+  }
+  int position = positions[t];
+  if (kind != 2 && rotary > 0) {
+    const int half = rotary >> 1;
+    int at = position;
+    if (at < 0 || at >= table_positions) {
+      if (lane == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+      at = 0;
+    }
+#pragma unroll
+    for (int i = 0; i < CNR_PER_LANE; ++i) staged[warp][lane + 32 * i] = y[i];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < CNR_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < rotary && e < size) {
+        const int pair = e < half ? e : e - half;
+        const float cs = cos_table[(size_t)at * half + pair], sn = sin_table[(size_t)at * half + pair];
+        const float other = staged[warp][e < half ? e + half : e - half];
+        y[i] = e < half ? y[i] * cs - other * sn : y[i] * cs + other * sn;
+      }
+    }
+  }
+  if (kind == 0) {
+    T* dst = q_out + (size_t)t * ld_q + (size_t)head * dim;
+#pragma unroll
+    for (int i = 0; i < CNR_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < size) dst[e] = from_float<T>(y[i]);
+    }
+    return;
+  }
+  if (!store) return;
+  const int page_index = position / page_size;
+  const int page = (position >= 0 && page_index < max_pages) ? block_table[(size_t)seq * max_pages + page_index] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (lane == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+    return;
+  }
+  T* dst = (kind == 1 ? k_pages : v_pages) + (((size_t)page * kv_heads + head) * page_size + position % page_size) * size;
+#pragma unroll
+  for (int i = 0; i < CNR_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    if (e < size) dst[e] = from_float<T>(y[i]);
+  }
+}
+
+// The convolution state after the step: the last taps-1 projected rows of each request, oldest first.  One thread
+// per (request, channel) reads what it needs before it writes, so a portion shorter than the state shifts it.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ raw, long long ld, float* __restrict__ conv_state,
+                                         const int* __restrict__ slots, const int* __restrict__ q_start, int taps,
+                                         int channels) {
+  const int seq = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int keep = taps - 1;
+  const int first = q_start[seq], n = q_start[seq + 1] - first;
+  if (n <= 0 || keep <= 0) return;
+  float* mine = conv_state + (size_t)slots[seq] * keep * channels + c;
+  float old[MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) old[j] = j < keep ? mine[(size_t)j * channels] : 0.0f;
+#pragma unroll
+  for (int j = 0; j < MAX_TAPS; ++j) {
+    if (j < keep) {
+      const int at = n + j;                                // in (old state, then this step's rows)
+      mine[(size_t)j * channels] = at < keep ? old[at] : to_float<T>(raw[(size_t)(first + at - keep) * ld + c]);
+    }
+  }
+}
+
+// The mean key and mean value of every block of `pool` positions whose last token this step brings: one block of
+// threads per (token, kv head); only tokens at a block's last position do anything.  The means are taken over the
+// keys and values as their pages hold them, and entry b of a request lies where position b would in the pooled pages.
+template <typename T>
+__global__ void __launch_bounds__(128) pool_kv_kernel(
+    const T* __restrict__ k_pages, const T* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
+    int num_pages, T* __restrict__ kp_pages, T* __restrict__ vp_pages, const int* __restrict__ pool_table,
+    int pool_max_pages, int pool_num_pages, int page_size, const int* __restrict__ positions,
+    const int* __restrict__ seq_of_token, int kv_heads, int dim, int vdim, int pool, int* status) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int position = positions[t];
+  if (position < 0 || (position + 1) % pool != 0) return;
+  const int seq = seq_of_token[t];
+  const int entry = (position + 1) / pool - 1;
+  const int entry_page = entry / page_size;
+  const int out_page = entry_page < pool_max_pages ? pool_table[(size_t)seq * pool_max_pages + entry_page] : -1;
+  if (out_page < 0 || out_page >= pool_num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+    return;
+  }
+  for (int e = threadIdx.x; e < dim + vdim; e += blockDim.x) {
+    const bool is_key = e < dim;
+    const int size = is_key ? dim : vdim, d = is_key ? e : e - dim;
+    const T* pages = is_key ? k_pages : v_pages;
+    float sum = 0.0f;
+    bool ok = true;
+    for (int p = position - pool + 1; p <= position; ++p) {
+      const int page_index = p / page_size;
+      const int page = page_index < max_pages ? block_table[(size_t)seq * max_pages + page_index] : -1;
+      if (page < 0 || page >= num_pages) { ok = false; break; }
+      sum += to_float<T>(pages[(((size_t)page * kv_heads + head) * page_size + p % page_size) * size + d]);
+    }
+    if (!ok) {
+      atomicOr(status, TGE_STATUS_BAD_PAGE);
+      continue;
+    }
+    T* dst = (is_key ? kp_pages : vp_pages) + (((size_t)out_page * kv_heads + head) * page_size + entry % page_size) * size + d;
+    *dst = from_float<T>(sum / (float)pool);
+  }
+}
+
+template <typename T>
+int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
+                      int activation, const float* cos_table, const float* sin_table, int table_positions, int rotary,
+                      float k_scale, const float* decay, float* state, const int* slots, const int* q_start,
+                      const int* positions, float* out, int num_seqs, int* status, cudaStream_t stream) {
+  dim3 grid((vdim + 31) / 32, heads, num_seqs);
+  const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_WARPS * SCAN_TOKENS * 32) * sizeof(float);
+  const int per_warp = (dim + SCAN_WARPS - 1) / SCAN_WARPS;
+#define TGE_SCAN(ROWS)                                                                                            \
+  decay_scan_kernel<T, ROWS><<<grid, SCAN_WARPS * 32, smem, stream>>>(                                            \
+      (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table, table_positions, \
+      rotary, k_scale, decay, state, slots, q_start, positions, out, status)
+  if (per_warp <= 8) TGE_SCAN(8);
+  else if (per_warp <= 16) TGE_SCAN(16);
+  else if (per_warp <= 32) TGE_SCAN(32);
+  else TGE_SCAN(64);
+#undef TGE_SCAN
+  return tge_launched("decay_scan", 1);
+}
+
+}  // namespace
+
+TGE_API int tge_to_run_dtype(const float* x, void* out, int is_bf16, long long count, cudaStream_t stream) {
+  TGE_REQUIRE(count >= 0, "to_run_dtype: negative count");
+  if (count == 0) return 0;
+  const unsigned blocks = (unsigned)((count + 255) / 256);
+  if (is_bf16) to_run_dtype_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (__nv_bfloat16*)out, (size_t)count);
+  else to_run_dtype_kernel<float><<<blocks, 256, 0, stream>>>(x, (float*)out, (size_t)count);
+  return tge_launched("to_run_dtype", 1);
+}
+
+TGE_API int tge_scale_add_norm(float* x, const float* y, long long ldy, const float* weight, void* copy, int copy_is_bf16,
+                               int rows, int hidden, float alpha, float eps, cudaStream_t stream) {
+  TGE_REQUIRE(rows >= 0 && hidden > 0 && ldy >= hidden, "scale_add_norm: bad shape (%d rows of %d)", rows, hidden);
+  TGE_REQUIRE(eps > 0.0f, "scale_add_norm: eps must be positive");
+  if (rows == 0) return 0;
+  if (copy != nullptr && copy_is_bf16)
+    scale_add_norm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(x, y, ldy, weight, (__nv_bfloat16*)copy, hidden, alpha, eps);
+  else
+    scale_add_norm_kernel<float><<<rows, 256, 0, stream>>>(x, y, ldy, weight, (float*)copy, hidden, alpha, eps);
+  return tge_launched("scale_add_norm", 1);
+}
+
+TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_off, int k_off, int v_off, int heads,
+                           int dim, int vdim, int activation, const float* cos_table, const float* sin_table,
+                           int table_positions, int rotary, float k_scale, const float* decay, float* state,
+                           const int* slots, const int* q_start, const int* positions, float* out, int num_seqs,
+                           int tokens, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && dim <= 64 * SCAN_WARPS, "decay_scan: %d heads of %d x %d (keys up to %d)",
+              heads, dim, vdim, 64 * SCAN_WARPS);
+  TGE_REQUIRE(rotary >= 0 && rotary % 2 == 0 && rotary <= dim, "decay_scan: %d rotated elements of %d", rotary, dim);
+  TGE_REQUIRE(rotary == 0 || (cos_table != nullptr && sin_table != nullptr && table_positions > 0),
+              "decay_scan: a rotation needs its tables");
+  TGE_REQUIRE(num_seqs >= 0 && num_seqs <= 65535 && heads <= 65535, "decay_scan: %d requests in a step", num_seqs);
+  if (num_seqs == 0 || tokens == 0) return 0;
+  if (is_bf16)
+    return launch_decay_scan<__nv_bfloat16>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table,
+                                            sin_table, table_positions, rotary, k_scale, decay, state, slots, q_start,
+                                            positions, out, num_seqs, status, stream);
+  return launch_decay_scan<float>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,
+                                  table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, num_seqs,
+                                  status, stream);
+}
+
+TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long long ld_gate, const float* weight, void* out,
+                           long long ld_out, int tokens, int groups, int size, float eps, int act, cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && groups > 0 && size > 0, "gated_norm: bad shape");
+  TGE_REQUIRE(act == 0 || act == 1, "gated_norm: the gate is silu (0) or sigmoid (1)");
+  if (tokens == 0) return 0;
+  const long long units = (long long)tokens * groups;
+  const unsigned blocks = (unsigned)((units + 3) / 4);
+  if (is_bf16)
+    gated_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, ld_gate, weight,
+                                                                  (__nv_bfloat16*)out, ld_out, tokens, groups, size, eps, act);
+  else
+    gated_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, ld_gate, weight, (float*)out, ld_out,
+                                                          tokens, groups, size, eps, act);
+  return tge_launched("gated_norm", 1);
+}
+
+TGE_API int tge_conv_norm_rope_store(const void* raw, int is_bf16, long long ld, const float* conv_w, int taps,
+                                     float* conv_state, const int* slots, const int* q_start, const float* q_norm,
+                                     const float* k_norm, float eps, const float* cos_table, const float* sin_table,
+                                     int table_positions, int rotary, const int* positions, const int* seq_of_token,
+                                     const int* block_table, int max_pages, void* k_pages, void* v_pages, int num_pages,
+                                     int page_size, void* q_out, long long ld_q, int tokens, int num_seqs, int heads,
+                                     int kv_heads, int dim, int vdim, int store, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && dim <= 32 * CNR_PER_LANE && vdim <= 32 * CNR_PER_LANE,
+              "conv_norm_rope_store: head sizes %d and %d outside (0, %d]", dim, vdim, 32 * CNR_PER_LANE);
+  TGE_REQUIRE(taps >= 0 && taps <= MAX_TAPS, "conv_norm_rope_store: %d taps (at most %d)", taps, MAX_TAPS);
+  TGE_REQUIRE(taps <= 1 || conv_state != nullptr, "conv_norm_rope_store: a convolution needs its state");
+  TGE_REQUIRE(taps == 0 || conv_w != nullptr, "conv_norm_rope_store: a convolution needs its weights");
+  TGE_REQUIRE(rotary >= 0 && rotary % 2 == 0 && rotary <= dim, "conv_norm_rope_store: %d rotated elements of %d", rotary, dim);
+  TGE_REQUIRE(rotary == 0 || (cos_table != nullptr && sin_table != nullptr && table_positions > 0),
+              "conv_norm_rope_store: a rotation needs its tables");
+  TGE_REQUIRE(!store || (page_size > 0 && max_pages > 0 && num_pages > 0), "conv_norm_rope_store: bad page geometry");
+  if (tokens == 0) return 0;
+  const int units = heads + 2 * kv_heads;
+  const int channels = (heads + kv_heads) * dim + kv_heads * vdim;
+  dim3 grid(tokens, (units + 3) / 4);
+  int launched = 1;
+  if (is_bf16) {
+    conv_norm_rope_store_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+        (const __nv_bfloat16*)raw, ld, conv_w, taps, conv_state, slots, q_start, q_norm, k_norm, eps, cos_table, sin_table,
+        table_positions, rotary, positions, seq_of_token, block_table, max_pages, (__nv_bfloat16*)k_pages,
+        (__nv_bfloat16*)v_pages, num_pages, page_size, (__nv_bfloat16*)q_out, ld_q, heads, kv_heads, dim, vdim, store, status);
+  } else {
+    conv_norm_rope_store_kernel<float><<<grid, 128, 0, stream>>>(
+        (const float*)raw, ld, conv_w, taps, conv_state, slots, q_start, q_norm, k_norm, eps, cos_table, sin_table,
+        table_positions, rotary, positions, seq_of_token, block_table, max_pages, (float*)k_pages, (float*)v_pages,
+        num_pages, page_size, (float*)q_out, ld_q, heads, kv_heads, dim, vdim, store, status);
+  }
+  if (int rc = tge_check_launch("conv_norm_rope_store")) return rc;
+  if (taps > 1) {
+    // in stream order behind the kernel that read the old state
+    dim3 update((channels + 127) / 128, num_seqs);
+    if (is_bf16)
+      conv_state_update_kernel<__nv_bfloat16><<<update, 128, 0, stream>>>((const __nv_bfloat16*)raw, ld, conv_state, slots,
+                                                                          q_start, taps, channels);
+    else
+      conv_state_update_kernel<float><<<update, 128, 0, stream>>>((const float*)raw, ld, conv_state, slots, q_start, taps,
+                                                                  channels);
+    ++launched;
+  }
+  return tge_launched("conv_state_update", launched);
+}
+
+TGE_API int tge_pool_kv(const void* k_pages, const void* v_pages, int is_bf16, const int* block_table, int max_pages,
+                        int num_pages, void* kp_pages, void* vp_pages, const int* pool_table, int pool_max_pages,
+                        int pool_num_pages, int page_size, const int* positions, const int* seq_of_token, int tokens,
+                        int kv_heads, int dim, int vdim, int pool, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(pool > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0, "pool_kv: bad shape");
+  if (tokens == 0) return 0;
+  dim3 grid(tokens, kv_heads);
+  if (is_bf16)
+    pool_kv_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages, num_pages,
+        (__nv_bfloat16*)kp_pages, (__nv_bfloat16*)vp_pages, pool_table, pool_max_pages, pool_num_pages, page_size, positions,
+        seq_of_token, kv_heads, dim, vdim, pool, status);
+  else
+    pool_kv_kernel<float><<<grid, 128, 0, stream>>>((const float*)k_pages, (const float*)v_pages, block_table, max_pages,
+                                                     num_pages, (float*)kp_pages, (float*)vp_pages, pool_table,
+                                                     pool_max_pages, pool_num_pages, page_size, positions, seq_of_token,
+                                                     kv_heads, dim, vdim, pool, status);
+  return tge_launched("pool_kv", 1);
+}

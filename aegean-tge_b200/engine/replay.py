@@ -68,7 +68,7 @@ def main(argv: Optional[list] = None) -> int:
     print(f"[trace_run] loading {args.model} ({args.dtype}); kernels are compiled on first use", file=sys.stderr,
           flush=True)
     engine = Engine(args.model, dtype=args.dtype, context=args.max_tokens, max_tokens=args.max_tokens,
-                    max_requests=8, max_batch_tokens=max(args.max_tokens, 1))
+                    max_requests=4, max_batch_tokens=max(args.max_tokens, 1))
     print(f"[trace_run] ready: {engine.describe()}", file=sys.stderr, flush=True)
     if args.trace:
         with open(args.trace, "r", encoding="utf-8") as handle:

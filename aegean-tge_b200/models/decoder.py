@@ -30,6 +30,10 @@ class DecoderModel:
         self.head = build_part(HEADS, spec.head, env)
         self.blocks: List[Block] = []
         for layer in spec.layers:
+            if layer.weights_from is not None:
+                # the same parts once more: parts hold weights only, what a layer keeps lives in its LayerCache
+                self.blocks.append(self.blocks[layer.weights_from])
+                continue
             mixer = build_part(MIXERS, layer.mixer, env)
             ffn = build_part(FEED_FORWARDS, layer.feed_forward, env) if layer.feed_forward is not None else None
             norm1 = build_part(NORMS, layer.mixer_norm, env)
@@ -49,6 +53,8 @@ class DecoderModel:
                                                  ("final_norm", self.final_norm, self.spec.final_norm),
                                                  ("head", self.head, self.spec.head)]
         for index, (block, layer) in enumerate(zip(self.blocks, self.spec.layers)):
+            if layer.weights_from is not None:
+                continue
             out.append((f"layers[{index}].mixer_norm", block.mixer_norm, layer.mixer_norm))
             out.append((f"layers[{index}].mixer", block.mixer, layer.mixer))
             if block.ffn_norm is not None:
@@ -83,8 +89,9 @@ class DecoderModel:
                     raise KeyError(f"{where}.{local}: tensor '{name}' was not loaded")
             if mine or part.param_specs():
                 part.load(mine)
-        for block in self.blocks:
-            block.loaded()
+        for block, layer in zip(self.blocks, self.spec.layers):
+            if layer.weights_from is None:
+                block.loaded()
 
     def step_param_bytes(self) -> int:
         """Bytes of parameters one step reads: every part once per visit, the embedding rows not counted."""
@@ -97,7 +104,8 @@ class DecoderModel:
     def declare_cache(self, manager: CacheManager) -> None:
         for index, (block, layer) in enumerate(zip(self.blocks, self.spec.layers)):
             if layer.cache_from is None:
-                manager.add_layer(index, block.mixer.cache_spec(), block.mixer.state_spec())
+                manager.add_layer(index, block.mixer.cache_spec(), block.mixer.state_spec(),
+                                  block.mixer.extra_cache_specs())
             else:
                 manager.add_layer(index, None, block.mixer.state_spec())
 

@@ -92,7 +92,23 @@ def core() -> ctypes.CDLL:
         lib.tge_gemm_tcgen05_scratch_floats.restype = _c_ll
         _declare(lib, "tge_attention_simt", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
-                                             _c_float, _c_int, _c_int, _c_ptr, _c_ptr])
+                                             _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                             _c_ptr, _c_ptr])
+        _declare(lib, "tge_to_run_dtype", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
+        _declare(lib, "tge_scale_add_norm", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float,
+                                             _c_float, _c_ptr])
+        _declare(lib, "tge_decay_scan", [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                         _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                         _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_gated_norm", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
+                                         _c_float, _c_int, _c_ptr])
+        _declare(lib, "tge_conv_norm_rope_store", [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                                                   _c_ptr, _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
+                                                   _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ll, _c_int,
+                                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_pool_kv", [_c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                                      _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                      _c_ptr])
         _declare(lib, "tge_qk_norm_kv_store", [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_int, _c_ptr, _c_int,
                                                _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int,
                                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
@@ -689,7 +705,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               num_seqs: int, max_q_len: int, max_ctx_len: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int = 0, split_tokens: int = 0, out: Optional[torch.Tensor] = None,
               force_simt: bool = False, typical_ctx_len: int = 0, decode_prefix: int = 0,
-              sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+              sink: Optional[torch.Tensor] = None, pool: int = 0, pooled_k: Optional[torch.Tensor] = None,
+              pooled_v: Optional[torch.Tensor] = None, pool_table: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged causal attention of a flat batch of portions.
 
     q: [T, >= heads*head_dim] (dense rows, any row stride) holding rotated queries;
@@ -701,6 +718,10 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     that are attended in parallel and merged; 0 picks a value from the batch shape.
     ``decode_prefix``: how many sequences at the head of the batch are known to bring one token each
     while others bring more (0: unknown); the tensor-core path then serves them with its decode kernel.
+    ``pool`` > 0 (with a window): beside the last ``window`` tokens a query sees one pooled key and value for
+    every block of ``pool`` positions that lies wholly before them, in the same softmax; ``pooled_k`` /
+    ``pooled_v`` are pages shaped like the keys' and values', entry b of a request where position b would be, found
+    through ``pool_table``.  Served by the CUDA-core kernel.
     """
     _want(q, "queries", _FLOAT, contiguous=False)
     q_stride = _rows_2d(q, "queries")
@@ -728,7 +749,19 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     # the tensor-core kernels read and write pairs of bfloat16: rows that start on odd elements (an inner buffer
     # whose neighbour has an odd width, say) go to the CUDA-core kernel
     pairs_ok = (q_stride % 2 == 0 and out_stride % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
-    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
+    pool_pages = pool_width = 0
+    if pool:
+        if window <= 0 or pooled_k is None or pooled_v is None or pool_table is None:
+            raise KernelError("attention: pooled blocks need a window, their pages and their table")
+        _want(pooled_k, "pooled k pages", q.dtype)
+        _want(pooled_v, "pooled v pages", q.dtype)
+        _want(pool_table, "pooled block table", torch.int32)
+        if (tuple(pooled_k.shape[1:]) != (kv_heads, page_size, head_dim)
+                or tuple(pooled_v.shape[1:]) != (kv_heads, page_size, value_dim) or pooled_k.shape[0] != pooled_v.shape[0]):
+            raise KernelError(f"pooled pages must be shaped like the keys' and values', got {tuple(pooled_k.shape)} "
+                              f"and {tuple(pooled_v.shape)}")
+        pool_pages, pool_width = pooled_k.shape[0], pool_table.shape[1]
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok and not pool
                and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim))
     if use_mma:
         lib = attention_lib(head_dim, value_dim)
@@ -757,8 +790,193 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                   block_table.data_ptr(), max_pages, num_pages, page_size, positions.data_ptr(),
                                   seq_of_token.data_ptr(), out.data_ptr(), out_stride, tokens, heads, kv_heads,
                                   head_dim, value_dim, _ptr(sink), float(scale), window, int(q.dtype == torch.bfloat16),
+                                  int(pool), _ptr(pooled_k), _ptr(pooled_v), _ptr(pool_table), pool_width, pool_pages,
                                   status_word().data_ptr(), _stream()), lib)
     return out
+
+
+def to_run_dtype(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 rows ``x`` in the format the products read (``x`` itself when that is float32)."""
+    _want(x, "rows", torch.float32)
+    if dtype == torch.float32:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    lib = core()
+    _check(lib.tge_to_run_dtype(x.data_ptr(), out.data_ptr(), 1, x.numel(), _stream()), lib)
+    return out
+
+
+def scale_add_norm(x: torch.Tensor, y: torch.Tensor, alpha: float, weight: torch.Tensor, eps: float,
+                   dtype: torch.dtype) -> torch.Tensor:
+    """The stream of a layer that normalises after the sum: x <- rms(alpha x + y) * weight, in place on the float32
+    rows ``x`` (``y`` float32, dense rows).  Returns the new rows in ``dtype`` for the next product (``x`` itself
+    when that is float32)."""
+    _want(x, "stream", torch.float32)
+    _want(y, "addend", torch.float32, contiguous=False)
+    _want(weight, "norm weight", torch.float32)
+    rows, hidden = x.shape
+    if tuple(y.shape) != (rows, hidden) or weight.numel() != hidden:
+        raise KernelError(f"scale_add_norm: stream {tuple(x.shape)}, addend {tuple(y.shape)}, weight {weight.numel()}")
+    copy = None if dtype == torch.float32 else torch.empty((rows, hidden), dtype=dtype, device=x.device)
+    lib = core()
+    _check(lib.tge_scale_add_norm(x.data_ptr(), y.data_ptr(), _rows_2d(y, "addend"), weight.data_ptr(), _ptr(copy),
+                                  int(copy is not None), rows, hidden, float(alpha), float(eps), _stream()), lib)
+    return x if copy is None else copy
+
+
+def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
+               decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, q_start: torch.Tensor,
+               positions: torch.Tensor, num_seqs: int, activation: bool = False, cos: Optional[torch.Tensor] = None,
+               sin: Optional[torch.Tensor] = None, rotary: int = 0, k_scale: float = 1.0) -> torch.Tensor:
+    """Linear attention with a fixed decay per head over a flat batch of portions, its state carried per request.
+
+    ``rows`` [T, ...] (run dtype, dense rows) holds the projections: q at column ``q_off`` and k at ``k_off``
+    (heads x dim each), v at ``v_off`` (heads x vdim).  q, k and v pass through SiLU first if ``activation``; q and
+    k are rotated over their first ``rotary`` elements (tables float32 [positions, rotary/2]); k is multiplied by
+    ``k_scale``.  Per head S <- decay S + k v^T and o = S^T q, token by token in float32; ``state`` is float32
+    [slots, heads, dim, vdim], read and written in the row ``slots[s]`` of each portion.  Returns o, float32
+    [T, heads*vdim]."""
+    _want(rows, "projections", _FLOAT, contiguous=False)
+    ld = _rows_2d(rows, "projections")
+    tokens = rows.shape[0]
+    _want(decay, "decay", torch.float32)
+    _want(state, "state", torch.float32)
+    for name, t in (("slots", slots), ("q_start", q_start), ("positions", positions)):
+        _want(t, name, torch.int32)
+    if decay.numel() != heads or state.dim() != 4 or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError(f"decay_scan: state must be [slots, {heads}, {dim}, {vdim}], got {tuple(state.shape)}; "
+                          f"decay has {decay.numel()} elements")
+    if max(q_off, k_off) + heads * dim > rows.shape[1] or v_off + heads * vdim > rows.shape[1]:
+        raise KernelError("decay_scan: the projections' rows are too short for the given offsets")
+    table_positions = 0
+    if rotary > 0:
+        _want(cos, "cos table", torch.float32)
+        _want(sin, "sin table", torch.float32)
+        if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != rotary // 2:
+            raise KernelError(f"rotary tables must be [positions, {rotary // 2}], got {tuple(cos.shape)}")
+        table_positions = cos.shape[0]
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=rows.device)
+    lib = core()
+    _check(lib.tge_decay_scan(rows.data_ptr(), int(rows.dtype == torch.bfloat16), ld, q_off, k_off, v_off, heads, dim,
+                              vdim, int(activation), _ptr(cos) if rotary else None, _ptr(sin) if rotary else None,
+                              table_positions, rotary, float(k_scale), decay.data_ptr(), state.data_ptr(),
+                              slots.data_ptr(), q_start.data_ptr(), positions.data_ptr(), out.data_ptr(), num_seqs, tokens,
+                              status_word().data_ptr(), _stream()), lib)
+    return out
+
+
+def gated_norm(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], groups: int, eps: float,
+               sigmoid: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = o / rms(o) * weight * act(gate), the root mean square taken over each of ``groups`` equal runs of a
+    row (one per head, or 1: all heads together).  ``o`` float32 [T, n]; ``gate`` run dtype [T, n] (dense rows, any
+    row stride); ``weight`` float32 [n] or None; act is SiLU, or the logistic function with ``sigmoid``."""
+    _want(o, "readout", torch.float32)
+    _want(gate, "gate", _FLOAT, contiguous=False)
+    tokens, width = o.shape
+    if tuple(gate.shape) != (tokens, width) or width % groups:
+        raise KernelError(f"gated_norm: readout {tuple(o.shape)}, gate {tuple(gate.shape)}, {groups} groups")
+    if weight is not None:
+        _want(weight, "norm weight", torch.float32)
+        if weight.numel() != width:
+            raise KernelError(f"gated_norm: weight has {weight.numel()} elements for rows of {width}")
+    if out is None:
+        out = torch.empty((tokens, width), dtype=gate.dtype, device=o.device)
+    _want(out, "gated_norm output", gate.dtype, contiguous=False)
+    lib = core()
+    _check(lib.tge_gated_norm(o.data_ptr(), gate.data_ptr(), int(gate.dtype == torch.bfloat16), _rows_2d(gate, "gate"),
+                              _ptr(weight), out.data_ptr(), _rows_2d(out, "gated_norm output"), tokens, groups,
+                              width // groups, float(eps), int(sigmoid), _stream()), lib)
+    return out
+
+
+def conv_norm_rope_store(raw: torch.Tensor, conv_w: Optional[torch.Tensor], taps: int, conv_state: Optional[torch.Tensor],
+                         slots: torch.Tensor, q_start: torch.Tensor, num_seqs: int, q_norm: Optional[torch.Tensor],
+                         k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor],
+                         sin: Optional[torch.Tensor], rotary: int, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                         block_table: Optional[torch.Tensor], k_pages: Optional[torch.Tensor],
+                         v_pages: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """What lies between the q/k/v product and the attention when the projections pass through a short causal
+    convolution over time: y_t = sum_j w[:, j] u_(t - taps + 1 + j) on every channel (``conv_w`` float32 [channels,
+    taps]; inputs from before the portion come from ``conv_state`` float32 [slots, taps-1, channels], which is then
+    brought up to date), an RMS norm of each q and k head (weights float32 [dim], None: none), the rotation of their
+    first ``rotary`` elements, and the store of k and v into their pages (None: nothing is stored).  ``raw`` [T, q | k
+    | v] in the run dtype.  Returns the queries [T, heads*dim].  ``taps`` 0: no convolution."""
+    _want(raw, "projections", _FLOAT, contiguous=False)
+    ld = _rows_2d(raw, "projections")
+    tokens = raw.shape[0]
+    channels = (heads + kv_heads) * dim + kv_heads * vdim
+    if raw.shape[1] < channels:
+        raise KernelError(f"conv_norm_rope_store: rows of {raw.shape[1]} for {channels} channels")
+    if taps:
+        _want(conv_w, "convolution weights", torch.float32)
+        if tuple(conv_w.shape) != (channels, taps):
+            raise KernelError(f"convolution weights must be [{channels}, {taps}], got {tuple(conv_w.shape)}")
+        if taps > 1:
+            _want(conv_state, "convolution state", torch.float32)
+            if conv_state.dim() != 3 or tuple(conv_state.shape[1:]) != (taps - 1, channels):
+                raise KernelError(f"convolution state must be [slots, {taps - 1}, {channels}], got {tuple(conv_state.shape)}")
+    for name, t in (("slots", slots), ("q_start", q_start), ("positions", positions), ("seq_of_token", seq_of_token)):
+        _want(t, name, torch.int32)
+    for name, t in (("q norm weight", q_norm), ("k norm weight", k_norm)):
+        if t is not None:
+            _want(t, name, torch.float32)
+            if t.numel() != dim:
+                raise KernelError(f"{name} has {t.numel()} elements for heads of {dim}")
+    table_positions = 0
+    if rotary > 0:
+        _want(cos, "cos table", torch.float32)
+        _want(sin, "sin table", torch.float32)
+        if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != rotary // 2:
+            raise KernelError(f"rotary tables must be [positions, {rotary // 2}], got {tuple(cos.shape)}")
+        table_positions = cos.shape[0]
+    store = k_pages is not None
+    num_pages = page_size = max_pages = 0
+    if store:
+        _want(k_pages, "k pages", raw.dtype)
+        _want(v_pages, "v pages", raw.dtype)
+        _want(block_table, "block table", torch.int32)
+        num_pages, _, page_size, _ = k_pages.shape
+        if (tuple(k_pages.shape) != (num_pages, kv_heads, page_size, dim)
+                or tuple(v_pages.shape) != (num_pages, kv_heads, page_size, vdim)):
+            raise KernelError(f"pages must be [pages, {kv_heads}, page_size, {dim} | {vdim}], got "
+                              f"{tuple(k_pages.shape)} and {tuple(v_pages.shape)}")
+        max_pages = block_table.shape[1]
+    q_out = torch.empty((tokens, heads * dim), dtype=raw.dtype, device=raw.device)
+    lib = core()
+    _check(lib.tge_conv_norm_rope_store(raw.data_ptr(), int(raw.dtype == torch.bfloat16), ld, _ptr(conv_w) if taps else None,
+                                        int(taps), _ptr(conv_state) if taps > 1 else None, slots.data_ptr(),
+                                        q_start.data_ptr(), _ptr(q_norm), _ptr(k_norm), float(eps),
+                                        _ptr(cos) if rotary else None, _ptr(sin) if rotary else None, table_positions,
+                                        rotary, positions.data_ptr(), seq_of_token.data_ptr(), _ptr(block_table), max_pages,
+                                        _ptr(k_pages), _ptr(v_pages), num_pages, page_size, q_out.data_ptr(), heads * dim,
+                                        tokens, num_seqs, heads, kv_heads, dim, vdim, int(store),
+                                        status_word().data_ptr(), _stream()), lib)
+    return q_out
+
+
+def pool_kv(k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor, pooled_k: torch.Tensor,
+            pooled_v: torch.Tensor, pool_table: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+            pool: int) -> None:
+    """For every token of the step that is the last of a block of ``pool`` positions: the mean of the block's keys
+    and of its values as the pages hold them, written as entry (position + 1) / pool - 1 of the request's pooled
+    pages.  Pages [pages, kv_heads, page_size, dim | vdim]; both tables int32 [S, width]."""
+    _want(k_pages, "k pages", _FLOAT)
+    _want(v_pages, "v pages", k_pages.dtype)
+    _want(pooled_k, "pooled k pages", k_pages.dtype)
+    _want(pooled_v, "pooled v pages", k_pages.dtype)
+    for name, t in (("block table", block_table), ("pooled block table", pool_table), ("positions", positions),
+                    ("seq_of_token", seq_of_token)):
+        _want(t, name, torch.int32)
+    num_pages, kv_heads, page_size, dim = k_pages.shape
+    vdim = v_pages.shape[3]
+    if tuple(pooled_k.shape[1:]) != (kv_heads, page_size, dim) or tuple(pooled_v.shape[1:]) != (kv_heads, page_size, vdim):
+        raise KernelError("pool_kv: pooled pages must be shaped like the keys' and values'")
+    lib = core()
+    _check(lib.tge_pool_kv(k_pages.data_ptr(), v_pages.data_ptr(), int(k_pages.dtype == torch.bfloat16),
+                           block_table.data_ptr(), block_table.shape[1], num_pages, pooled_k.data_ptr(),
+                           pooled_v.data_ptr(), pool_table.data_ptr(), pool_table.shape[1], pooled_k.shape[0], page_size,
+                           positions.data_ptr(), seq_of_token.data_ptr(), positions.numel(), kv_heads, dim, vdim, int(pool),
+                           status_word().data_ptr(), _stream()), lib)
 
 
 # Fewer leading single-token sequences than this ride along in the prefill kernel: each fills one query tile,

@@ -17,6 +17,18 @@ learned score per head that joins the softmax's denominator with no key or
 value behind it (``sinks``); and a blend of the values with those that an
 earlier layer computed for the same token (``value_mix``).  With a norm or a
 blend, one kernel normalises, blends and stores after the q/k/v product.
+
+Two more, for designs that bound what a request keeps: a short causal
+convolution over time on every channel of q, k and v right after the
+projection (``short_conv``; its last inputs are per-request state), and,
+with a window, pooled blocks (``pool``): beside the window's tokens a query
+sees the mean key and mean value of every block of that many positions that
+lies wholly before the window.  The pooled entries live in pages of their
+own, one entry per block, so the tokens' pages can be given back once the
+window and the block in the making have passed them.  Either option, or a
+rotation with values of another size than the keys, takes the general path:
+product, then one kernel that convolves, normalises, rotates and stores,
+one that pools, and the attention.
 """
 from __future__ import annotations
 
@@ -25,7 +37,7 @@ from typing import Dict, Optional
 import torch
 
 from ..config.model_spec import PartSpec
-from .base import (MIXERS, POSITIONS, LayerCache, Mixer, PagedCacheSpec, ParamSpec, StepContext, build_part)
+from .base import (MIXERS, POSITIONS, LayerCache, Mixer, PagedCacheSpec, ParamSpec, StateSpec, StepContext, build_part)
 
 
 @MIXERS.register("gqa_attention")
@@ -35,9 +47,11 @@ class GQAttention(Mixer):
     ``position`` (a PartSpec), optional ``scale``; optional ``value_dim`` (default ``head_dim``),
     ``qk_norm`` (None, or ``{"scope": "projection" | "head", "eps": e}``), ``sinks`` (bool),
     ``value_mix`` (None, ``"first"``: this layer's values are kept for the step under ``value_mix_key``, or
-    ``"blend"``: v <- (1 - w) v + w v_first with the learned scalar w).
+    ``"blend"``: v <- (1 - w) v + w v_first with the learned scalar w); ``short_conv`` (None or the number of taps),
+    ``pool`` (None or the pooled blocks' size; needs a window).
     weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``; ``q_norm.weight`` / ``k_norm.weight``
-    (float32, the projection's or one head's size); ``sink`` [heads]; ``value_mix.weight`` (a scalar).
+    (float32, the projection's or one head's size); ``sink`` [heads]; ``value_mix.weight`` (a scalar);
+    ``q|k|v.conv.weight`` (float32 [channels, taps]).
     """
     graph_safe = True
     can_defer_norm = True
@@ -70,6 +84,12 @@ class GQAttention(Mixer):
         self.value_mix_key = ("value_mix", str(p.get("value_mix_key", "values")))
         if self.value_dim <= 0:
             raise ValueError("attention: value_dim must be positive")
+        self.taps = int(p.get("short_conv") or 0)
+        self.pool = int(p.get("pool") or 0)
+        if self.taps < 0 or self.taps > 8:
+            raise ValueError(f"attention: a short convolution has 1 to 8 taps, not {self.taps}")
+        if self.pool < 0 or (self.pool and self.window is None):
+            raise ValueError("attention: pooled blocks need a positive size and a window")
         position: PartSpec = p.get("position", PartSpec("none"))
         self.position = build_part(POSITIONS, position, env)
         self.graph_safe = bool(self.position.graph_safe)
@@ -81,8 +101,15 @@ class GQAttention(Mixer):
         self.plain = self.qk_norm is None and self.value_mix is None and self.value_dim == self.head_dim
         tables = self.position.rotary_tables()
         self.rotates = tables is None or tables[2] > 0
-        if self.value_dim != self.head_dim and self.rotates:
-            raise ValueError("attention: the rotate-and-store kernel needs values of the keys' size")
+        # the general path: convolution, per-head norm, rotation and store in one kernel, pooled blocks
+        self.general = bool(self.taps or self.pool or (self.value_dim != self.head_dim and self.rotates))
+        if self.general:
+            if self.value_mix is not None or self.qkv_bias or (self.qk_norm is not None and self.qk_norm[0] != "head"):
+                raise ValueError("attention: a short convolution, pooled blocks, or a rotation with values of their own "
+                                 "size go with a per-head q/k norm or none, without biases on q, k, v or value mixing")
+            if tables is None:
+                raise ValueError("attention: the general path rotates by tables, or not at all")
+        self.conv_w: Optional[torch.Tensor] = None
         self.q_norm_w: Optional[torch.Tensor] = None
         self.k_norm_w: Optional[torch.Tensor] = None
         self.sink: Optional[torch.Tensor] = None
@@ -111,6 +138,10 @@ class GQAttention(Mixer):
             # only a blending layer uses the scalar; a checkpoint may hold one for the other layers too (the first
             # of a chain, layers that do not mix), so a model spec may name it for them and it is then optional
             specs["value_mix.weight"] = ParamSpec((), role="vector", optional=self.value_mix != "blend")
+        if self.taps:
+            specs["q.conv.weight"] = ParamSpec((self.q_dim, self.taps), role="vector")
+            specs["k.conv.weight"] = ParamSpec((self.kv_dim, self.taps), role="vector")
+            specs["v.conv.weight"] = ParamSpec((self.v_dim, self.taps), role="vector")
         if self.qkv_bias:
             specs["q.bias"] = ParamSpec((self.q_dim,), role="vector")
             specs["k.bias"] = ParamSpec((self.kv_dim,), role="vector")
@@ -131,6 +162,9 @@ class GQAttention(Mixer):
             self.k_norm_w = tensors["k_norm.weight"].contiguous()
         if self.sinks:
             self.sink = tensors["sink"].contiguous()
+        if self.taps:
+            self.conv_w = torch.cat([tensors["q.conv.weight"], tensors["k.conv.weight"], tensors["v.conv.weight"]],
+                                    dim=0).contiguous()
         if self.value_mix == "blend":
             self.mix_w = tensors["value_mix.weight"].reshape(1).contiguous()
 
@@ -139,15 +173,56 @@ class GQAttention(Mixer):
         return products + 2.0 * self.heads * (self.head_dim + self.value_dim) * pairs     # scores and weighted values
 
     def cache_spec(self) -> Optional[PagedCacheSpec]:
+        # with pooled blocks a token is also read when its block is averaged, which is when the block's last token
+        # arrives: the pages keep whichever reaches further back, the window or a block
+        window = None if self.window is None else max(int(self.window), self.pool)
         return PagedCacheSpec(entries=(("k", (self.kv_heads, self.head_dim)), ("v", (self.kv_heads, self.value_dim))),
-                              window=None if self.window is None else int(self.window))
+                              window=window)
+
+    def extra_cache_specs(self) -> Dict[str, PagedCacheSpec]:
+        if not self.pool:
+            return {}
+        return {"pooled": PagedCacheSpec(entries=(("k", (self.kv_heads, self.head_dim)), ("v", (self.kv_heads, self.value_dim))),
+                                         window=None, stride=self.pool)}
+
+    def state_spec(self) -> Optional[StateSpec]:
+        if self.taps > 1:
+            return StateSpec(entries=(("conv", (self.taps - 1, self.q_dim + self.kv_dim + self.v_dim)),))
+        return None
+
+    def attend_general(self, h, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Product; convolution, per-head norm, rotation and store; pooled blocks; attention."""
+        ops = self.ops
+        k_pages, v_pages = cache.paged["k"], cache.paged["v"]
+        table = ctx.block_tables[cache.group]
+        cos, sin, rotary = self.position.rotary_tables()
+        raw = ops.linear(h, self.w_qkv, None, ops.GEMM_STORE)
+        q = ops.conv_norm_rope_store(raw, self.conv_w, self.taps, cache.state.get("conv"), ctx.slots, ctx.q_start,
+                                     ctx.num_seqs, self.q_norm_w, self.k_norm_w, self.qk_norm[1] if self.qk_norm else 1.0,
+                                     cos, sin, rotary, ctx.positions, ctx.seq_of_token, table,
+                                     k_pages if cache.owner else None, v_pages if cache.owner else None,
+                                     self.heads, self.kv_heads, self.head_dim, self.value_dim)
+        pooled = {}
+        if self.pool:
+            more = cache.more["pooled"]
+            pool_table = ctx.block_tables[more.group]
+            if cache.owner:
+                ops.pool_kv(k_pages, v_pages, table, more.paged["k"], more.paged["v"], pool_table, ctx.positions,
+                            ctx.seq_of_token, self.pool)
+            pooled = {"pool": self.pool, "pooled_k": more.paged["k"], "pooled_v": more.paged["v"], "pool_table": pool_table}
+        return ops.attention(q, k_pages, v_pages, table, ctx.q_start, ctx.start_pos, ctx.positions, ctx.seq_of_token,
+                             ctx.num_seqs, ctx.max_q_len, ctx.max_ctx_len, self.heads, self.kv_heads, self.head_dim,
+                             self.scale, window=int(self.window or 0), split_tokens=ctx.attn_split_tokens,
+                             typical_ctx_len=ctx.typical_ctx_len, decode_prefix=ctx.decode_prefix, sink=self.sink,
+                             out=out, **pooled)
 
     def share_input_projection(self, rows: torch.Tensor) -> Optional[torch.Tensor]:
         """A block offers the rows of another product over the same input (a feed-forward's up weight) to be
         multiplied together with q, k and v.  A mixer whose small-batch kernel can carry them (whole-projection
         q/k norm, no rotation, no biases) puts them below its own rows in one tensor and returns the view that now
         holds them (the caller uses it in place of its copy); None: it cannot."""
-        if self.plain or self.rotates or self.qkv_bias or (self.qk_norm is not None and self.qk_norm[0] != "projection"):
+        if (self.plain or self.general or self.rotates or self.qkv_bias
+                or (self.qk_norm is not None and self.qk_norm[0] != "projection")):
             return None
         if self.w_qkv is None or rows.dtype != self.w_qkv.dtype or rows.shape[1] != self.hidden:
             return None
@@ -162,6 +237,9 @@ class GQAttention(Mixer):
 
         ``beside``: (output view, epilogue) for the rows that :meth:`share_input_projection` took in; the result is
         then a pair (rows, whether the shared rows were multiplied and activated here)."""
+        if self.general:
+            a = self.attend_general(h, ctx, cache, out=out)
+            return a if beside is None else (a, False)
         ops = self.ops
         k_pages, v_pages = cache.paged["k"], cache.paged["v"]
         table = ctx.block_tables[cache.group]
@@ -241,6 +319,11 @@ class GQAttention(Mixer):
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         return self.ops.linear(self.attend(h, ctx, cache), self.w_o, self.b_o, self.ops.GEMM_STORE)
+
+    def forward_f32(self, h, ctx: StepContext, cache: LayerCache, out=None, alpha: float = 1.0, accumulate: bool = False):
+        a = self.attend(h, ctx, cache)
+        epilogue = self.ops.GEMM_ADD_F32 if accumulate else self.ops.GEMM_STORE_F32
+        return self.ops.linear(a, self.w_o, self.b_o, epilogue, out=out, alpha=alpha)
 
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache, next_norm=None,
                     defer: bool = False):

@@ -53,14 +53,17 @@ class PagedCacheSpec:
     attention ``{"k": (kv_heads, head_dim), "v": (kv_heads, head_dim)}``.
     ``window`` is None when every earlier token stays readable, else the
     number of most recent tokens (the current one included) a query may read;
-    pages wholly behind the window are given back.
+    pages wholly behind the window are given back.  ``stride`` > 1: one entry per
+    block of that many positions (pooled keys and values), kept once the block
+    is whole; entry b of a request then sits where position b would.
     """
 
     entries: Tuple[Tuple[str, Tuple[int, ...]], ...]
     window: Optional[int] = None
+    stride: int = 1
 
     def group_key(self) -> Tuple:
-        return (self.entries, self.window)
+        return (self.entries, self.window, self.stride)
 
 
 @dataclass(frozen=True)
@@ -90,6 +93,7 @@ class LayerCache:
     group: Optional[int] = None                                    # index of its page group
     state: Dict[str, torch.Tensor] = field(default_factory=dict)   # name -> [slots, ...]
     owner: bool = True                                             # False: reads another layer's cache, stores nothing
+    more: Dict[str, "LayerCache"] = field(default_factory=dict)    # further paged caches the mixer declared, by name
 
 
 @dataclass
@@ -206,6 +210,11 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def extra_cache_specs(self) -> Dict[str, PagedCacheSpec]:
+        """Paged caches beside the main one (``cache_spec``), by name: pooled entries, for instance, of which
+        there is one per block of positions.  The mixer finds them in ``cache.more[name]``."""
+        return {}
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         """h: run dtype [T, H] (already normed) -> [T, H] to be added to the stream."""
         raise NotImplementedError
@@ -220,6 +229,18 @@ class Mixer(Part):
     def output_projection(self) -> Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]]:
         """(weight [H, inner width], bias or None) of the last product, or None."""
         return None
+
+    def forward_f32(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache, out: Optional[torch.Tensor] = None,
+                    alpha: float = 1.0, accumulate: bool = False) -> torch.Tensor:
+        """``out`` (float32 [T, H]) = alpha * mixer(h), or += with ``accumulate``: what a layer that normalises after
+        its sum, or a mixer made of several, asks for.  The default goes through ``forward``; a mixer that ends in a
+        product writes float32 from its epilogue."""
+        if out is None or not accumulate:
+            if out is None:
+                out = torch.empty((h.shape[0], self.env.hidden_size), dtype=torch.float32, device=h.device)
+            out.zero_()
+        self.ops.add_to_stream(out, self.forward(h, ctx, cache), alpha=alpha)
+        return out
 
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: LayerCache,
                     next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:
@@ -245,6 +266,12 @@ class FeedForward(Part):
 
     def output_projection(self) -> Optional[Tuple[torch.Tensor, Optional[torch.Tensor]]]:
         return None
+
+    def forward_f32(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """The feed-forward's output in float32 [T, H] (see ``Mixer.forward_f32``)."""
+        out = torch.zeros((h.shape[0], self.env.hidden_size), dtype=torch.float32, device=h.device)
+        self.ops.add_to_stream(out, self.forward(h, ctx))
+        return out
 
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext,
                     next_norm: Optional["Norm"] = None) -> Optional[torch.Tensor]:

@@ -117,3 +117,34 @@ class ParallelBlock(Block):
                                        defer=bool(next_takes_deferred), alpha=self.mult)
         ops.linear(inner, self.w_out, self.b_out, ops.GEMM_ADD_F32, out=x, alpha=self.mult)
         return None
+
+
+@BLOCKS.register("post_norm")
+class PostNormBlock(Block):
+    """x <- norm1(a x + mixer(x)); x <- norm2(a x + ffn(x)): the norm comes after the sum, and the sublayers
+    read the stream itself.
+
+    params: ``alpha`` (a, default 1).  The feed-forward and its norm may be absent.  The stream stays float32; the
+    kernel that normalises it also writes the rows the next product reads, so a sublayer's input is never normed
+    on its own.  ``forward`` returns those rows for the next layer.
+    """
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, env, params=None):
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, env, params)
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("post-norm block: a feed-forward and its norm come together")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and norm.fusable() is None:
+                raise ValueError("post-norm block: its norms are plain RMS norms")
+        self.alpha = float(self.params.get("alpha", 1.0))
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None):
+        ops = self.env.ops
+        if h is None:
+            h = ops.to_run_dtype(x, self.env.dtype)
+        weight, eps = self.mixer_norm.fusable()
+        h = ops.scale_add_norm(x, self.mixer.forward_f32(h, ctx, cache), self.alpha, weight, eps, self.env.dtype)
+        if self.feed_forward is not None:
+            weight, eps = self.ffn_norm.fusable()
+            h = ops.scale_add_norm(x, self.feed_forward.forward_f32(h, ctx), self.alpha, weight, eps, self.env.dtype)
+        return h

@@ -50,6 +50,10 @@ class SwiGLU(FeedForward):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
         return self.ops.linear(a, self.w_down, None, self.ops.GEMM_STORE)
 
+    def forward_f32(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
+        return self.ops.linear(a, self.w_down, None, self.ops.GEMM_STORE_F32)
+
     def forward_add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext, next_norm=None, defer: bool = False):
         a = self.ops.linear(h, self.w_gate_up, None, self.ops.GEMM_SWIGLU)
         fused = next_norm.fusable() if next_norm is not None else None

@@ -15,6 +15,7 @@ routine returns.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional, Tuple
 
 import torch
@@ -22,12 +23,39 @@ import torch
 from .base import POSITIONS, PositionEncoding
 
 
-def rotary_tables(theta: float, rotary: int, positions: int) -> Tuple[torch.Tensor, torch.Tensor]:
+def rescale_by_wavelength(freq: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """Frequencies (float64) slowed down for long wavelengths: with l = 2 pi / f, f is kept where
+    l < original / high, divided by ``factor`` where l > original / low, and between the two blended,
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    wavelength = 2.0 * math.pi / freq
+    s = (original / wavelength - low) / (high - low)
+    blended = (1.0 - s) * freq / factor + s * freq
+    out = torch.where(wavelength > original / low, freq / factor, blended)
+    return torch.where(wavelength < original / high, freq, out)
+
+
+def rotary_tables(theta: float, rotary: int, positions: int,
+                  scaling: Optional[Tuple[float, float, float, float]] = None,
+                  precise: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of position * frequency, float32 [positions, rotary/2].  By default the exponent, the
+    frequency and the angle are each rounded to float32 as described above; with ``precise`` all of it is
+    float64 and only the cosine and the sine are rounded (an angle of a thousand radians in float32 is already
+    off by 6e-5)."""
     half = rotary // 2
+    if precise:
+        index = torch.arange(half, dtype=torch.float64)
+        freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * index / float(rotary))
+        if scaling is not None:
+            freq = rescale_by_wavelength(freq, *scaling)
+        angle = torch.arange(positions, dtype=torch.float64)[:, None] * freq[None, :]
+        return torch.cos(angle).float(), torch.sin(angle).float()
     index = torch.arange(half, dtype=torch.float32)
     exponent = (-2.0 * index) / torch.tensor(float(rotary), dtype=torch.float32)          # float32
     theta32 = torch.tensor(theta, dtype=torch.float32)
-    freq = torch.pow(theta32.double(), exponent.double()).float()                           # rounded once
+    freq = torch.pow(theta32.double(), exponent.double())
+    if scaling is not None:
+        freq = rescale_by_wavelength(freq, *scaling)
+    freq = freq.float()                                                                     # rounded once
     angle = torch.arange(positions, dtype=torch.float32)[:, None] * freq[None, :]          # float32 product
     return torch.cos(angle.double()).float(), torch.sin(angle.double()).float()
 
@@ -37,7 +65,9 @@ _TABLES: dict = {}
 
 @POSITIONS.register("rope_neox")
 class RotaryNeoX(PositionEncoding):
-    """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default head_dim)."""
+    """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default head_dim), optional ``scaling``
+    (``{"factor", "low", "high", "original"}``: frequencies rescaled by wavelength, see
+    :func:`rescale_by_wavelength`), optional ``precise`` (tables from float64 angles)."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -49,12 +79,20 @@ class RotaryNeoX(PositionEncoding):
             raise ValueError(f"rope: rotary width {self.rotary} must be even and within head_dim {self.head_dim}")
         if not self.theta > 0:
             raise ValueError("rope: theta must be positive")
+        scaling = spec.params.get("scaling")
+        self.scaling = None
+        if scaling is not None:
+            self.scaling = tuple(float(scaling[name]) for name in ("factor", "low", "high", "original"))
+            factor, low, high, original = self.scaling
+            if not (factor > 0 and original > 0 and high > low >= 0):
+                raise ValueError(f"rope: scaling {scaling!r} needs factor > 0, original > 0 and high > low >= 0")
         # layers with the same base, width and length share one pair of tables
-        key = (self.theta, self.rotary, env.max_positions, str(env.device))
+        self.precise = bool(spec.params.get("precise", False))
+        key = (self.theta, self.rotary, env.max_positions, str(env.device), self.scaling, self.precise)
         if key not in _TABLES:
             if len(_TABLES) >= 8:
                 _TABLES.pop(next(iter(_TABLES)))
-            cos, sin = rotary_tables(self.theta, self.rotary, env.max_positions)
+            cos, sin = rotary_tables(self.theta, self.rotary, env.max_positions, self.scaling, self.precise)
             _TABLES[key] = (cos.to(env.device).contiguous(), sin.to(env.device).contiguous())
         self.cos, self.sin = _TABLES[key]
 

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "tge_rt_cache_create": (c_void_p, [c_int, c_int]),
     "tge_rt_cache_destroy": (None, [c_void_p]),
     "tge_rt_cache_add_group": (c_int, [c_void_p, c_int]),
+    "tge_rt_cache_add_group_strided": (c_int, [c_void_p, c_int, c_int]),
     "tge_rt_cache_set_pool_size": (c_int, [c_void_p, c_int, c_int]),
     "tge_rt_cache_pool": (c_void_p, [c_void_p, c_int]),
     "tge_rt_cache_groups": (c_int, [c_void_p]),
