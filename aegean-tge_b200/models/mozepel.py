@@ -55,7 +55,7 @@ def _window_part(m: WindowAttention, width: int, eps: float, prefix: str) -> Tup
         weights.update({f"{t}.conv.weight": f"{prefix}{t}.conv" for t in ("q", "k", "v")})
     params = {"hidden_size": width, "heads": m.heads, "kv_heads": m.kv_heads, "head_dim": m.dim, "value_dim": m.vdim,
               "scale": m.scale, "qkv_bias": False, "o_bias": False, "window": m.window, "pool": m.pool or None,
-              "short_conv": m.conv or None, "position": _position(m.rot, m.dim), "qk_norm": {"scope": "head", "eps": eps}}
+              "short_conv": m.conv or None, "prepare_in_one_kernel": True, "position": _position(m.rot, m.dim), "qk_norm": {"scope": "head", "eps": eps}}
     return PartSpec("gqa_attention", params, weights), weights
 
 

@@ -48,7 +48,8 @@ class GQAttention(Mixer):
     ``qk_norm`` (None, or ``{"scope": "projection" | "head", "eps": e}``), ``sinks`` (bool),
     ``value_mix`` (None, ``"first"``: this layer's values are kept for the step under ``value_mix_key``, or
     ``"blend"``: v <- (1 - w) v + w v_first with the learned scalar w); ``short_conv`` (None or the number of taps),
-    ``pool`` (None or the pooled blocks' size; needs a window).
+    ``pool`` (None or the pooled blocks' size; needs a window), ``prepare_in_one_kernel`` (bool: take the general path,
+    one kernel between the product and the attention, whatever the options).
     weights: ``q|k|v|o.weight`` and, with the bias flags, ``q|k|v|o.bias``; ``q_norm.weight`` / ``k_norm.weight``
     (float32, the projection's or one head's size); ``sink`` [heads]; ``value_mix.weight`` (a scalar);
     ``q|k|v.conv.weight`` (float32 [channels, taps]).
@@ -102,7 +103,8 @@ class GQAttention(Mixer):
         tables = self.position.rotary_tables()
         self.rotates = tables is None or tables[2] > 0
         # the general path: convolution, per-head norm, rotation and store in one kernel, pooled blocks
-        self.general = bool(self.taps or self.pool or (self.value_dim != self.head_dim and self.rotates))
+        self.general = bool(p.get("prepare_in_one_kernel") or self.taps or self.pool
+                            or (self.value_dim != self.head_dim and self.rotates))
         if self.general:
             if self.value_mix is not None or self.qkv_bias or (self.qk_norm is not None and self.qk_norm[0] != "head"):
                 raise ValueError("attention: a short convolution, pooled blocks, or a rotation with values of their own "

@@ -105,10 +105,11 @@ def retention(x: np.ndarray, w: Dict[str, np.ndarray], prefix: str, m: dict, eps
     k = (x @ w[prefix + "k"].astype(F).T).reshape(T, H, d)
     v = (x @ w[prefix + "v"].astype(F).T).reshape(T, H, dv)
     gate = x @ w[prefix + "g"].astype(F).T
-    positions = np.arange(T)
-    freq = frequencies(m["rot"]["dims"], m["rot"]["base"])
-    q = rotate(q, positions, m["rot"]["dims"], freq)
-    k = rotate(k, positions, m["rot"]["dims"], freq) * d ** -0.5
+    if m.get("rot"):
+        freq = frequencies(m["rot"]["dims"], m["rot"]["base"])
+        q = rotate(q, np.arange(T), m["rot"]["dims"], freq)
+        k = rotate(k, np.arange(T), m["rot"]["dims"], freq)
+    k = k * d ** -0.5
     o = unit_rms(decayed_state_readout(q, k, v, m["decay"]), eps).reshape(T, H * dv)
     return (o * silu(gate)) @ w[prefix + "o"].astype(F).T
 
@@ -118,7 +119,7 @@ def window_pool_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: fl
     (positions b pool .. b pool + pool - 1, by its mean key and mean value) if b pool + pool - 1 <= i - size."""
     T, H, _ = q.shape
     G = k.shape[1]
-    blocks = T // pool
+    blocks = T // pool if pool else 0
     kp = np.stack([k[b * pool:(b + 1) * pool].mean(axis=0) for b in range(blocks)]) if blocks else np.zeros((0,) + k.shape[1:])
     vp = np.stack([v[b * pool:(b + 1) * pool].mean(axis=0) for b in range(blocks)]) if blocks else np.zeros((0,) + v.shape[1:])
     out = np.zeros((T, H, v.shape[2]), dtype=F)
@@ -126,7 +127,7 @@ def window_pool_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: fl
         g = h // (H // G)
         for i in range(T):
             first = max(i - size + 1, 0)
-            seen = max((i - size + 1) // pool, 0)          # blocks whose last position is <= i - size
+            seen = max((i - size + 1) // pool, 0) if pool else 0     # blocks whose last position is <= i - size
             keys = np.concatenate([kp[:seen, g], k[first:i + 1, g]], axis=0)
             vals = np.concatenate([vp[:seen, g], v[first:i + 1, g]], axis=0)
             s = scale * (keys @ q[i, h])
@@ -138,16 +139,17 @@ def window_pool_attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: fl
 def left_branch(x: np.ndarray, w: Dict[str, np.ndarray], prefix: str, m: dict, eps: float) -> np.ndarray:
     T = x.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = short_conv(x @ w[prefix + "q"].astype(F).T, w[prefix + "q.conv"]).reshape(T, H, d)
-    k = short_conv(x @ w[prefix + "k"].astype(F).T, w[prefix + "k.conv"]).reshape(T, G, d)
-    v = short_conv(x @ w[prefix + "v"].astype(F).T, w[prefix + "v.conv"]).reshape(T, G, dv)
-    q = rms_norm(q, w[prefix + "q.norm"], eps)
-    k = rms_norm(k, w[prefix + "k.norm"], eps)
-    positions = np.arange(T)
-    freq = frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
-    q = rotate(q, positions, m["rot"]["dims"], freq)
-    k = rotate(k, positions, m["rot"]["dims"], freq)
-    a = window_pool_attention(q, k, v, m["scale"], m["mask"]["size"], m["mask"]["pool"])
+    q, k, v = (x @ w[prefix + name].astype(F).T for name in ("q", "k", "v"))
+    if m.get("conv"):
+        q, k, v = (short_conv(u, w[f"{prefix}{name}.conv"]) for u, name in ((q, "q"), (k, "k"), (v, "v")))
+    q = rms_norm(q.reshape(T, H, d), w[prefix + "q.norm"], eps)
+    k = rms_norm(k.reshape(T, G, d), w[prefix + "k.norm"], eps)
+    v = v.reshape(T, G, dv)
+    if m.get("rot"):
+        freq = frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
+        q = rotate(q, np.arange(T), m["rot"]["dims"], freq)
+        k = rotate(k, np.arange(T), m["rot"]["dims"], freq)
+    a = window_pool_attention(q, k, v, m["scale"], m["mask"]["size"], m["mask"].get("pool") or 0)
     return a.reshape(T, H * dv) @ w[prefix + "o"].astype(F).T
 
 

@@ -1,0 +1,701 @@
+"""The Mozepel design in the engine against its plain implementation (tests/plain/mozepel_plain.py).
+
+First every mechanism alone through its kernel (the decayed state with its rotation and activation, the gated norms,
+the short convolution with its per-request tail, the per-head norm and rotation before the store, pooled blocks and
+the window in one softmax, the norm after the sum), with inputs made so that a key one place off, a block seen too
+early or a lost state shows; then whole models of five small configurations that differ in every size, order and
+option, cut and batched in every way, both number formats.
+"""
+import copy
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_error
+from plain import mozepel_plain as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = ["float32", "bfloat16"]
+KERNEL_TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+MODEL_TOL = {"float32": 3e-5, "bfloat16": 4e-2}
+# In bfloat16 the first tokens of a request are the hard ones: the state then holds one or two outer products, a
+# head's readout is (q . k) v with a dot product that may nearly cancel, and the norm that follows divides by it.
+# The smallest configuration (heads of 12, width 100) shows it most: largest error seen 5.7e-2.
+BFLOAT16_TOL = {"C": 9e-2}
+
+
+def _tol(name, dtype):
+    return BFLOAT16_TOL.get(name, MODEL_TOL[dtype]) if dtype == "bfloat16" else MODEL_TOL[dtype]
+
+
+def _rot(base, dims, scaling=None):
+    out = {"base": base, "dims": dims}
+    if scaling:
+        out["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    return out
+
+
+def _retention(heads, dim, vdim, decay, rot, ff, weights_of=None):
+    entry = {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "rot": rot},
+             "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+    if weights_of is not None:
+        entry["weights_of"] = weights_of
+    return entry
+
+
+def _parallel(left, right, left_scale, right_scale, ff, weights_of=None):
+    entry = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": left_scale, "right_scale": right_scale},
+             "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+    if weights_of is not None:
+        entry["weights_of"] = weights_of
+    return entry
+
+
+def _left(heads, kv_heads, dim, vdim, scale, conv, size, pool, rot):
+    out = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": size, "pool": pool},
+           "rot": rot}
+    if conv:
+        out["conv"] = conv
+    return out
+
+
+def _right(heads, dim, vdim, decay):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay}
+
+
+def _config(vocab, width, eps, alpha, layers):
+    return {"architecture": "Mozepel", "vocab": vocab, "width": width, "norm": {"eps": eps}, "postln_alpha": alpha, "layers": layers}
+
+
+def _configs():
+    a_par = _parallel(_left(4, 2, 32, 48, 0.2, 3, 24, 5, _rot(5000.0, 16, (4.0, 1.0, 3.0, 64))),
+                      _right(3, 16, 32, [0.7, 0.95, 0.999]), 0.8, 1.3, 96)
+    a_ret = _retention(3, 16, 48, [0.9, 0.97, 0.995], _rot(10000.0, 8), 80)
+    b_ret = _retention(2, 32, 32, [1.0, 0.5], _rot(100.0, 32), 64)
+    return {
+        # a parallel layer first; keys and values of unlike sizes everywhere; part of each head rotated; the third layer
+        # has no feed-forward; layers 3 and 4 run the tensors of layers 1 and 0 with a state and cache of their own
+        "A": _config(210, 64, 1e-5, 2.0, [a_par, a_ret, _retention(2, 32, 16, [0.99, 0.9], _rot(777.0, 32), None),
+                                           dict(copy.deepcopy(a_ret), weights_of=1), dict(copy.deepcopy(a_par), weights_of=0)]),
+        # what other models keep apart is equal or 1 here: alpha and both branch scales 1, as many kv heads as heads,
+        # one tap, blocks of one token, a decay of exactly 1, whole heads rotated, no frequency scaling
+        "B": _config(128, 96, 1e-6, 1.0, [b_ret, _parallel(_left(3, 3, 32, 32, 0.18, 1, 7, 1, _rot(300.0, 32)),
+                                                           _right(2, 16, 48, [0.9, 0.99]), 1.0, 1.0, 128)]),
+        # nothing a multiple of 8; a window shorter than a block; no convolution
+        "C": _config(97, 100, 2e-5, 0.7, [_parallel(_left(6, 2, 20, 12, 0.3, 0, 3, 11, _rot(50.0, 6, (2.0, 0.5, 2.0, 16))),
+                                                    _right(5, 12, 20, [0.8, 0.85, 0.9, 0.95, 0.99]), 1.5, 0.4, 70),
+                                          _retention(5, 20, 12, [0.6, 0.7, 0.8, 0.9, 0.99], _rot(9.0, 10), 30)]),
+        # heads of 64 and 128; eight taps; a window over several pages of 16
+        "D": _config(300, 128, 1e-6, 3.5, [_retention(2, 64, 128, [0.98, 0.995], _rot(500000.0, 64), 192),
+                                           _parallel(_left(4, 1, 128, 64, 0.09, 8, 50, 16, _rot(250000.0, 64, (8.0, 1.0, 4.0, 128))),
+                                                     _right(2, 128, 64, [0.9, 0.99]), 1.1, 0.6, 192)]),
+        # a window and blocks longer than the prompts of most tests: nothing is pooled until late
+        "E": _config(150, 48, 1e-5, 1.5, [_parallel(_left(2, 1, 16, 16, 0.25, 4, 130, 64, _rot(1000.0, 8)),
+                                                    _right(2, 8, 8, [0.5, 0.9]), 0.5, 2.0, None)]),
+    }
+
+
+CONFIGS = _configs()
+SEEDS = {"A": 21, "B": 22, "C": 23, "D": 24, "E": 25}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from aegean_tge_b200 import ops as module
+    return module
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from aegean_tge_b200 import write_random_model
+    out = {}
+    for name, config in CONFIGS.items():
+        folder = tmp_path_factory.mktemp(f"mozepel_{name}")
+        write_random_model(str(folder), config, seed=SEEDS[name], dtype="float32")
+        out[name] = str(folder)
+    return out
+
+
+def _read_weights(folder):
+    with open(os.path.join(folder, "model.safetensors"), "rb") as handle:
+        size = int.from_bytes(handle.read(8), "little")
+        header = json.loads(handle.read(size))
+        data = handle.read()
+    out = {}
+    for name, entry in header.items():
+        if name == "__metadata__":
+            continue
+        assert entry["dtype"] == "F32", (name, entry["dtype"])
+        begin, end = entry["data_offsets"]
+        out[name] = np.frombuffer(data[begin:end], dtype="<f4").reshape(entry["shape"]).copy()
+    return out
+
+
+def _to_bfloat16(array):
+    return torch.from_numpy(array).to(torch.bfloat16).float().numpy()
+
+
+@pytest.fixture(scope="module")
+def oracle(folders):
+    weights, cache = {}, {}
+
+    def get(name, dtype, tokens, config=None):
+        if (name, dtype) not in weights:
+            w = _read_weights(folders[name])
+            if dtype == "bfloat16":         # matrices are held in bfloat16, vectors (norms, taps) in float32
+                w = {k: (_to_bfloat16(v) if v.ndim == 2 and not k.endswith(".conv") else v) for k, v in w.items()}
+            weights[(name, dtype)] = w
+        key = (name, dtype, tuple(tokens), json.dumps(config, sort_keys=True) if config else "")
+        if key not in cache:
+            cache[key] = torch.from_numpy(plain.forward(config or CONFIGS[name], weights[(name, dtype)], list(tokens))).float()
+        return cache[key]
+    return get
+
+
+def _tokens(name, count, salt=0):
+    rnd = random.Random(SEEDS[name] * 1000 + salt)
+    return [rnd.randrange(CONFIGS[name]["vocab"]) for _ in range(count)]
+
+
+def _engine(folders, name, dtype, **kw):
+    from aegean_tge_b200 import Engine
+    kw.setdefault("context", 512)
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_requests", 8)
+    return Engine(folders[name], dtype=dtype, **kw)
+
+
+def _portion(request, tokens, want=None):
+    from aegean_tge_b200.engine import Portion
+    return Portion(request, tokens, list(range(len(tokens))) if want is None else want)
+
+
+def _i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+def _steps(cuts, starts=None):
+    """Index tensors of one step: portions of the given lengths that start at the given positions."""
+    starts = starts or [0] * len(cuts)
+    positions, seq, q_start = [], [], [0]
+    for s, (n, first) in enumerate(zip(cuts, starts)):
+        positions += list(range(first, first + n))
+        seq += [s] * n
+        q_start.append(q_start[-1] + n)
+    return _i32(positions), _i32(seq), _i32(q_start)
+
+
+# ---------------------------------------------------------------------------
+# mechanisms, one by one
+# ---------------------------------------------------------------------------
+def test_frequencies_rescaled_by_wavelength():
+    from aegean_tge_b200.parts.rope import rotary_tables
+    for dims, base, scaling in ((16, 5000.0, (4.0, 1.0, 3.0, 64)), (64, 250000.0, (8.0, 1.0, 4.0, 128)), (6, 50.0, (2.0, 0.5, 2.0, 16)),
+                                (32, 100.0, None)):
+        named = dict(zip(("factor", "low", "high", "original"), scaling)) if scaling else None
+        freq = plain.frequencies(dims, base, named)
+        if scaling:      # the three regimes all occur in at least one case; the blend is neither end
+            plain_freq = plain.frequencies(dims, base, None)
+            assert np.any(freq != plain_freq)
+        cos, sin = rotary_tables(base, dims, 700, scaling, precise=True)
+        angle = np.arange(700)[:, None] * freq[None, :]
+        assert np.abs(cos.numpy() - np.cos(angle)).max() < 2e-7 and np.abs(sin.numpy() - np.sin(angle)).max() < 2e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dim,vdim,rotary,activation,k_scale", [
+    (3, 16, 48, 8, False, 0.25), (2, 32, 32, 32, False, 32 ** -0.5), (5, 12, 20, 0, True, 1.0), (2, 128, 64, 0, True, 1.0),
+    (2, 64, 128, 64, False, 0.125), (1, 200, 70, 100, True, 0.5)])
+@pytest.mark.parametrize("cuts", [[[77]], [[40], [1], [1], [2], [33]], [[9, 1, 30], [8, 1, 30], [1, 1, 1]]])
+def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rotary, activation, k_scale, cuts):
+    """Requests cut into portions, each step a batch; the state lives in slots that are not in order."""
+    from aegean_tge_b200.parts.rope import rotary_tables
+    gen = torch.Generator().manual_seed(heads * 1000 + dim)
+    count = len(cuts[0])
+    lengths = [sum(step[s] for step in cuts) for s in range(count)]
+    decay = [1.0 - 0.5 ** (2 + h) for h in range(heads)]
+    decay[0] = 1.0 if heads > 1 else 0.9
+    width = 2 * heads * dim + heads * vdim + 5
+    data = [(torch.randn(n, width, generator=gen) * 0.7).to(dtype) for n in lengths]
+    cos, sin = rotary_tables(300.0, max(rotary, 2), 512, None, precise=True)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    slots = [5, 0, 3][:count]
+    state = torch.randn(7, heads, dim, vdim, device=DEV)          # stale junk in every slot
+    for slot in slots:
+        state[slot].zero_()
+    untouched = state[6].clone()
+    done = [0] * count
+    got = [[] for _ in range(count)]
+    for step in cuts:
+        rows = torch.cat([data[s][done[s]:done[s] + step[s]] for s in range(count)]).to(DEV)
+        positions, _seq, q_start = _steps(step, done)
+        out = ops.decay_scan(rows, 3, 3 + heads * dim, 5 + 2 * heads * dim, heads, dim, vdim,
+                             torch.tensor(decay, dtype=torch.float32, device=DEV), state, _i32(slots), q_start, positions, count,
+                             activation=activation, cos=cos, sin=sin, rotary=rotary, k_scale=k_scale)
+        at = 0
+        for s in range(count):
+            got[s].append(out[at:at + step[s]])
+            at += step[s]
+            done[s] += step[s]
+    ops.check_status()
+    assert torch.equal(state[6], untouched)
+    freq = plain.frequencies(max(rotary, 2), 300.0)
+    for s in range(count):
+        x = data[s].double().numpy()
+        n = lengths[s]
+        q = x[:, 3:3 + heads * dim].reshape(n, heads, dim)
+        k = x[:, 3 + heads * dim:3 + 2 * heads * dim].reshape(n, heads, dim)
+        v = x[:, 5 + 2 * heads * dim:5 + 2 * heads * dim + heads * vdim].reshape(n, heads, vdim)
+        if activation:
+            q, k, v = plain.silu(q), plain.silu(k), plain.silu(v)
+        if rotary:
+            q, k = plain.rotate(q, np.arange(n), rotary, freq), plain.rotate(k, np.arange(n), rotary, freq)
+        ref = plain.decayed_state_readout(q, k * k_scale, v, decay).reshape(n, heads * vdim)
+        assert rel_error(torch.cat(got[s]), torch.from_numpy(ref)) < 3e-5        # float32 arithmetic in both formats
+
+
+def test_a_lost_state_would_show(ops):
+    """With a decay of 1 the first token's key and value stay in every later readout: zeroing the state between two
+    portions changes the second portion's rows by far more than the tolerance."""
+    heads, dim, vdim = 2, 16, 16
+    gen = torch.Generator().manual_seed(3)
+    rows = torch.randn(20, 3 * heads * dim, generator=gen).to(DEV)
+    rows[0] *= 10.0
+    decay = torch.ones(heads, device=DEV)
+    outs = []
+    for lose in (False, True):
+        state = torch.zeros(2, heads, dim, vdim, device=DEV)
+        parts = []
+        for first, count in ((0, 12), (12, 8)):
+            positions, _seq, q_start = _steps([count], [first])
+            parts.append(ops.decay_scan(rows[first:first + count], 0, heads * dim, 2 * heads * dim, heads, dim, vdim, decay, state,
+                                        _i32([1]), q_start, positions, 1))
+            if lose:
+                state.zero_()
+        outs.append(torch.cat(parts))
+    assert torch.equal(outs[0][:12], outs[1][:12])
+    assert rel_error(outs[1][12:], outs[0][12:]) > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("groups,size,weighted,sigmoid", [(3, 48, False, False), (1, 160, True, True), (5, 12, True, False), (2, 256, False, True)])
+def test_gated_norm(ops, dtype, groups, size, weighted, sigmoid):
+    gen = torch.Generator().manual_seed(groups + size)
+    tokens, eps = 37, 1e-5
+    o = torch.randn(tokens, groups * size, generator=gen) * 3.0
+    wide = torch.randn(tokens, groups * size + 9, generator=gen).to(dtype)
+    weight = (1.0 + 0.1 * torch.randn(groups * size, generator=gen)) if weighted else None
+    got = ops.gated_norm(o.to(DEV), wide.to(DEV)[:, 9:], None if weight is None else weight.to(DEV), groups, eps, sigmoid)
+    normed = plain.unit_rms(o.double().numpy().reshape(tokens, groups, size), eps).reshape(tokens, groups * size)
+    if weighted:
+        normed = normed * weight.double().numpy()
+    gate = wide[:, 9:].double().numpy()
+    ref = normed * (plain.sigmoid(gate) if sigmoid else plain.silu(gate))
+    assert got.dtype == dtype and rel_error(got, torch.from_numpy(ref)) < KERNEL_TOL[dtype]
+
+
+@pytest.mark.parametrize("hidden", [48, 100, 1024])
+def test_norm_after_the_sum(ops, hidden):
+    gen = torch.Generator().manual_seed(hidden)
+    x, y = torch.randn(19, hidden, generator=gen), torch.randn(19, hidden, generator=gen)
+    weight = 1.0 + 0.1 * torch.randn(hidden, generator=gen)
+    ref = plain.rms_norm(2.5 * x.double().numpy() + y.double().numpy(), weight.numpy(), 1e-5)
+    for dtype in (torch.float32, torch.bfloat16):
+        stream = x.clone().to(DEV)
+        rows = ops.scale_add_norm(stream, y.to(DEV), 2.5, weight.to(DEV), 1e-5, dtype)
+        assert rel_error(stream, torch.from_numpy(ref)) < 2e-6
+        assert rows.dtype == dtype and rel_error(rows, torch.from_numpy(ref)) < KERNEL_TOL[dtype]
+        assert (rows.data_ptr() == stream.data_ptr()) == (dtype == torch.float32)
+
+
+def _paged(lengths, kv_heads, size, page_size, dtype, seed, extra=3):
+    """Empty pages (stale junk) for requests of the given lengths, on shuffled page ids: (pages, table)."""
+    need = [max(-(-n // page_size), 1) for n in lengths]
+    total = sum(need) + extra
+    order = list(range(total))
+    random.Random(seed).shuffle(order)
+    gen = torch.Generator().manual_seed(seed)
+    pages = torch.randn(total, kv_heads, page_size, size, generator=gen).to(dtype).to(DEV)
+    table = torch.full((len(lengths), max(need)), -1, dtype=torch.int32)
+    cursor = 0
+    for s, count in enumerate(need):
+        for j in range(count):
+            table[s, j] = order[cursor]
+            cursor += 1
+    return pages, table.to(DEV)
+
+
+def _gather(pages, table, s, n, page_size):
+    """[n, kv_heads, size] of request s from its pages."""
+    rows = [pages[int(table[s, p // page_size]), :, p % page_size] for p in range(n)]
+    return torch.stack(rows).float().cpu() if rows else torch.zeros(0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,rotary,normed", [
+    (4, 2, 32, 48, 3, 16, True), (3, 3, 32, 32, 1, 32, True), (6, 2, 20, 12, 0, 6, True), (4, 1, 128, 64, 8, 64, True), (2, 1, 16, 16, 4, 0, False)])
+@pytest.mark.parametrize("cuts", [[[50]], [[2], [1], [1], [2], [30], [3], [11]], [[20, 1, 2], [1, 2, 20], [29, 1, 1]]])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_convolution_norm_rotation_and_store(ops, dtype, heads, kv_heads, dim, vdim, taps, rotary, normed, cuts, page_size):
+    """Portions down to one token, so that a convolution's inputs come from the step, from the state, or from both."""
+    from aegean_tge_b200.parts.rope import rotary_tables
+    gen = torch.Generator().manual_seed(dim + taps)
+    count = len(cuts[0])
+    lengths = [sum(step[s] for step in cuts) for s in range(count)]
+    channels = (heads + kv_heads) * dim + kv_heads * vdim
+    raw = [torch.randn(n, channels + 4, generator=gen).to(dtype) for n in lengths]
+    conv_w = torch.randn(channels, max(taps, 1), generator=gen) if taps else None
+    q_norm = (1.0 + 0.2 * torch.randn(dim, generator=gen)) if normed else None
+    k_norm = (1.0 + 0.2 * torch.randn(dim, generator=gen)) if normed else None
+    eps = 1e-5
+    scaling = (4.0, 1.0, 3.0, 64.0)
+    cos, sin = rotary_tables(5000.0, max(rotary, 2), 256, scaling, precise=True)
+    k_pages, table = _paged(lengths, kv_heads, dim, page_size, dtype, 7)
+    v_pages, _ = _paged(lengths, kv_heads, vdim, page_size, dtype, 7)
+    slots = [4, 1, 2][:count]
+    state = torch.randn(6, max(taps - 1, 1), channels, device=DEV) if taps > 1 else None
+    if state is not None:
+        for slot in slots:
+            state[slot].zero_()
+    done = [0] * count
+    got_q = [[] for _ in range(count)]
+    dev = lambda t: None if t is None else t.to(DEV)
+    for step in cuts:
+        rows = torch.cat([raw[s][done[s]:done[s] + step[s]] for s in range(count)]).to(DEV)
+        positions, seq, q_start = _steps(step, done)
+        q = ops.conv_norm_rope_store(rows, dev(conv_w), taps, state, _i32(slots), q_start, count, dev(q_norm), dev(k_norm), eps,
+                                     cos.to(DEV), sin.to(DEV), rotary, positions, seq, table, k_pages, v_pages, heads, kv_heads, dim, vdim)
+        at = 0
+        for s in range(count):
+            got_q[s].append(q[at:at + step[s]])
+            at += step[s]
+            done[s] += step[s]
+    ops.check_status()
+    freq = plain.frequencies(max(rotary, 2), 5000.0, dict(zip(("factor", "low", "high", "original"), scaling)))
+    for s in range(count):
+        n = lengths[s]
+        u = raw[s][:, :channels].double().numpy()
+        y = plain.short_conv(u, conv_w.double().numpy()) if taps else u
+        q = y[:, :heads * dim].reshape(n, heads, dim)
+        k = y[:, heads * dim:(heads + kv_heads) * dim].reshape(n, kv_heads, dim)
+        v = y[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim)
+        if normed:
+            q, k = plain.rms_norm(q, q_norm.numpy(), eps), plain.rms_norm(k, k_norm.numpy(), eps)
+        if rotary:
+            q, k = plain.rotate(q, np.arange(n), rotary, freq), plain.rotate(k, np.arange(n), rotary, freq)
+        tol = KERNEL_TOL[dtype]
+        assert rel_error(torch.cat(got_q[s]).float().cpu().reshape(n, heads, dim), torch.from_numpy(q)) < tol
+        assert rel_error(_gather(k_pages, table, s, n, page_size), torch.from_numpy(k)) < tol
+        assert rel_error(_gather(v_pages, table, s, n, page_size), torch.from_numpy(v)) < tol
+        if taps > 1:        # the state is the last taps-1 projected rows, zeros where the request had none yet
+            tail = np.concatenate([np.zeros((taps - 1, channels)), u])[-(taps - 1):]
+            assert rel_error(state[slots[s]].cpu(), torch.from_numpy(tail)) < 1e-6
+
+
+def _window_pool_case(ops, dtype, heads, kv_heads, dim, vdim, size, pool, lengths, tails, page_size, spike=None):
+    """Requests of ``lengths`` whose last ``tails[s]`` tokens come in a second step (0: all at once).  Keys and
+    values are stored and pooled by the kernels; the queries of both steps are checked.  ``spike`` = (request, key
+    position, query position): that key and that query get one large matching element so that the score stands out."""
+    gen = torch.Generator().manual_seed(size * 100 + pool)
+    channels = (heads + kv_heads) * dim + kv_heads * vdim
+    raw = [torch.randn(n, channels, generator=gen).to(dtype) for n in lengths]
+    if spike is not None:
+        s, key_at, query_at = spike
+        raw[s][key_at, heads * dim:(heads + kv_heads) * dim] = 0.0
+        raw[s][key_at, heads * dim:(heads + kv_heads) * dim:dim] = 8.0          # element 0 of every kv head
+        raw[s][query_at, :heads * dim:dim] = 8.0
+    k_pages, table = _paged(lengths, kv_heads, dim, page_size, dtype, 9)
+    v_pages, _ = _paged(lengths, kv_heads, vdim, page_size, dtype, 9)
+    blocks = [n // pool for n in lengths]
+    kp_pages, ptable = _paged(blocks, kv_heads, dim, page_size, dtype, 10)
+    vp_pages, _ = _paged(blocks, kv_heads, vdim, page_size, dtype, 10)
+    count = len(lengths)
+    scale = 0.3
+    got = [[] for _ in range(count)]
+    done = [0] * count
+    for step in ([n - t for n, t in zip(lengths, tails)], tails):
+        who = [s for s in range(count) if step[s] > 0]
+        if not who:
+            continue
+        rows = torch.cat([raw[s][done[s]:done[s] + step[s]] for s in who]).to(DEV)
+        positions, seq, q_start = _steps([step[s] for s in who], [done[s] for s in who])
+        pick = torch.tensor(who, device=DEV)
+        tab, ptab = table[pick].contiguous(), ptable[pick].contiguous()
+        q = ops.conv_norm_rope_store(rows, None, 0, None, _i32([0] * len(who)), q_start, len(who), None, None, 1.0, None, None, 0,
+                                     positions, seq, tab, k_pages, v_pages, heads, kv_heads, dim, vdim)
+        ops.pool_kv(k_pages, v_pages, tab, kp_pages, vp_pages, ptab, positions, seq, pool)
+        start_pos = _i32([done[s] for s in who])
+        out = ops.attention(q, k_pages, v_pages, tab, q_start, start_pos, positions, seq, len(who), max(step), max(lengths), heads,
+                            kv_heads, dim, scale, window=size, pool=pool, pooled_k=kp_pages, pooled_v=vp_pages, pool_table=ptab)
+        at = 0
+        for s in who:
+            got[s].append(out[at:at + step[s]])
+            at += step[s]
+            done[s] += step[s]
+    ops.check_status()
+    errors = []
+    for s in range(count):
+        n = lengths[s]
+        x = raw[s].double().numpy()
+        q = x[:, :heads * dim].reshape(n, heads, dim)
+        k = x[:, heads * dim:(heads + kv_heads) * dim].reshape(n, kv_heads, dim)
+        v = x[:, (heads + kv_heads) * dim:].reshape(n, kv_heads, vdim)
+        ref = plain.window_pool_attention(q, k, v, scale, size, pool).reshape(n, heads * vdim)
+        errors.append((torch.cat(got[s]), torch.from_numpy(ref)))
+    return errors
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 32, 48), (3, 3, 32, 32), (6, 2, 20, 12), (4, 1, 128, 64)])
+@pytest.mark.parametrize("size,pool", [(24, 5), (7, 1), (3, 11), (50, 16), (64, 64)])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_window_and_pooled_blocks_in_one_softmax(ops, dtype, heads, kv_heads, dim, vdim, size, pool, page_size):
+    lengths, tails = [200, 67, 1, 130], [0, 30, 0, 1]
+    for got, ref in _window_pool_case(ops, dtype, heads, kv_heads, dim, vdim, size, pool, lengths, tails, page_size):
+        assert rel_error(got, ref) < KERNEL_TOL[dtype] * (2 if dtype == torch.bfloat16 else 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("tail", [0, 1, 40])
+@pytest.mark.parametrize("size,pool,page_size", [(24, 5, 16), (50, 16, 64), (64, 64, 64), (3, 11, 16)])
+def test_keys_at_every_edge_stand_out(ops, dtype, tail, size, pool, page_size):
+    """One key made to dominate its query's softmax, placed just inside the window, just outside it (seen through
+    its block or not at all), in the newest block that is seen and in the next one, at page borders and far back; in
+    a prompt and, with ``tail``, among tokens that come later.  The plain implementation with a window or a block
+    size that is one off differs by far more than the tolerance."""
+    n = 190
+    query = n - 1 if tail else n - 30
+    newest = (query - size + 1) // pool - 1                 # the newest block this query sees
+    places = {query - size + 1, query - size, (newest + 1) * pool - 1, (newest + 1) * pool, newest * pool, 0, 63, 64, query}
+    for key in sorted(p for p in places if 0 <= p <= query):
+        (got, ref), = _window_pool_case(ops, dtype, 4, 2, 32, 16, size, pool, [n], [tail], page_size, spike=(0, key, query))
+        assert rel_error(got, ref) < KERNEL_TOL[dtype] * (2 if dtype == torch.bfloat16 else 1), key
+    # the oracle itself tells a window or a block that is one off
+    gen = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(n, 2, 8, generator=gen).double().numpy() for _ in range(3))
+    k[query - size + 1] = 3.0 * q[query]
+    base = plain.window_pool_attention(q, k, v, 0.5, size, pool)
+    assert np.abs(plain.window_pool_attention(q, k, v, 0.5, size - 1, pool)[query] - base[query]).max() > 0.05
+    k[query - size + 1] = q[query - size + 1]
+    k[(newest + 1) * pool - 1] = 40.0 * q[query]
+    base = plain.window_pool_attention(q, k, v, 0.5, size, pool)
+    assert np.abs(plain.window_pool_attention(q, k, v, 0.5, size + pool, pool)[query] - base[query]).max() > 0.05
+
+
+# ---------------------------------------------------------------------------
+# whole models
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompts_and_first_tokens(folders, oracle, ops, name, dtype):
+    engine = _engine(folders, name, dtype)
+    for length in (1, 2, 3, 7, 16, 64, 65, 150):
+        tokens = _tokens(name, length, salt=length)
+        logits = engine.runner.step([_portion("r", tokens)])
+        engine.runner.finish("r")
+        assert rel_error(logits, oracle(name, dtype, tokens)) < _tol(name, dtype), (name, dtype, length)
+    ops.check_status()
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_each_mechanism_left_out_would_show(oracle, name):
+    """The oracle with a window or block one off, without the convolution, with other branch scales, another alpha or
+    a layer that does not share its weights' state differs from the model by far more than the tolerance."""
+    tokens = _tokens(name, 90, salt=77)
+    ref = oracle(name, "float32", tokens)
+    index = [i for i, layer in enumerate(CONFIGS[name]["layers"]) if layer["type"] == "parallel"][0]
+    for change in ("size", "pool", "left_scale", "right_scale", "alpha", "decay", "rot", "scaling") + (("conv",) if name == "A" else ()):
+        other = copy.deepcopy(CONFIGS[name])
+        mixers = [layer["mixer"] for layer in other["layers"] if layer["type"] == "parallel"]
+        for mixer in mixers:
+            if change in ("size", "pool"):
+                mixer["left"]["mask"][change] += 1
+            elif change in ("left_scale", "right_scale"):
+                mixer[change] *= 1.3
+            elif change == "decay":
+                mixer["right"]["decay"] = [min(c * 1.001, 1.0) ** 8 for c in mixer["right"]["decay"]]
+            elif change == "rot":
+                mixer["left"]["rot"]["base"] *= 2.0
+            elif change == "scaling":
+                mixer["left"]["rot"].pop("scaling")
+            elif change == "conv" and "conv" in mixer["left"]:
+                mixer["left"].pop("conv")
+        if change == "alpha":
+            other["postln_alpha"] *= 1.2
+        assert rel_error(oracle(name, "float32", tokens, other), ref) > 20 * MODEL_TOL["float32"], (change, index)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_prefill_against_token_by_token_decoding(folders, oracle, name, dtype):
+    tokens = _tokens(name, 110, salt=1)
+    ref = oracle(name, dtype, tokens)
+    engine = _engine(folders, name, dtype)
+    rows = [engine.runner.step([_portion("r", tokens[:68])])]
+    for t in range(68, len(tokens)):
+        rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+    got = torch.cat(rows)
+    assert rel_error(got, ref) < _tol(name, dtype)
+    if dtype == "float32":
+        whole = _engine(folders, name, dtype).runner.step([_portion("w", tokens)])
+        assert float((got - whole).abs().max()) <= 2e-5 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_portions_down_to_two_tokens(folders, oracle, name, dtype, page_size):
+    tokens = _tokens(name, 230, salt=2)
+    ref = oracle(name, dtype, tokens)
+    engine = _engine(folders, name, dtype, page_size=page_size)
+    cuts = [7, 2, 16, 3, 2, 30, 2, 17, 41, 1, 1, 26, 2, 64, 5, 2, 2, 7]
+    assert sum(cuts) == len(tokens)
+    rows, pos = [], 0
+    for count in cuts:
+        rows.append(engine.runner.step([_portion("r", tokens[pos:pos + count])]))
+        pos += count
+    assert rel_error(torch.cat(rows), ref) < _tol(name, dtype)
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("page_size,pool_tokens", [(16, 320), (64, 512)])
+def test_unequal_requests_in_one_batch_on_pages_and_slots_that_are_used_again(folders, oracle, ops, name, dtype, page_size,
+                                                                            pool_tokens):
+    """Up to four live requests in four slots, portions of some beside single tokens of others, a pool so small that
+    pages and slots of finished requests serve the next ones; every request's logits are those it gets alone."""
+    lengths = {"a": 70, "b": 45, "c": 130, "d": 19, "e": 64, "f": 33, "g": 90}
+    tokens = {r: _tokens(name, n, salt=ord(r)) for r, n in lengths.items()}
+    engine = _engine(folders, name, dtype, max_tokens=pool_tokens, page_size=page_size, max_requests=4)
+    got, done = {r: [] for r in lengths}, {r: 0 for r in lengths}
+    holders, slot_users = {}, {}
+
+    def run(step):
+        logits = engine.runner.step([_portion(r, tokens[r][done[r]:done[r] + count]) for r, count in step])
+        row = 0
+        for r, count in step:
+            got[r].append(logits[row:row + count])
+            row += count
+            done[r] += count
+            slot_users.setdefault(engine.cache.slot_of(r), set()).add(r)
+            for page in engine.cache.groups[0].tables[r]:
+                if page >= 0:
+                    holders.setdefault(page, set()).add(r)
+            if done[r] == lengths[r]:
+                engine.runner.finish(r)
+
+    run([("a", 40), ("b", 3)])
+    run([("a", 2), ("b", 40), ("c", 64), ("d", 1)])
+    run([("a", 28), ("b", 2), ("c", 2), ("d", 16)])          # a and b end
+    run([("c", 60), ("d", 2), ("e", 1), ("f", 30)])           # d ends; e and f take over pages and slots
+    for _ in range(3):
+        run([("c", 1), ("e", 1), ("f", 1)])                   # f ends
+    run([("c", 1), ("e", 58), ("g", 2)])
+    run([("e", 2), ("g", 64)])                                # c ended before; e ends
+    run([("g", 24)])
+    ops.check_status()
+    engine.cache.check()
+    assert any(len(who) > 1 for who in holders.values()) and any(len(who) > 1 for who in slot_users.values())
+    assert not engine.cache.live_requests()
+    for r in lengths:
+        assert done[r] == lengths[r]
+        assert rel_error(torch.cat(got[r]), oracle(name, dtype, tokens[r])) < _tol(name, dtype), (name, dtype, r)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
+def test_long_decoding_past_windows_and_blocks(folders, oracle, name, dtype):
+    """Three tokens of prompt, then 330 single tokens through the decode graphs: the window and many pooled blocks
+    pass over decoded tokens, the window's pages are given back on the way."""
+    tokens = _tokens(name, 333, salt=5)
+    ref = oracle(name, dtype, tokens)
+    engine = _engine(folders, name, dtype, page_size=16)
+    rows = [engine.runner.step([_portion("r", tokens[:3])])]
+    for t in range(3, len(tokens)):
+        rows.append(engine.runner.step([_portion("r", tokens[t:t + 1])]))
+    assert rel_error(torch.cat(rows), ref) < _tol(name, dtype)
+    assert engine.runner.graph_replays > 0
+    windowed = [g for g in engine.cache.groups if g.spec.window is not None]
+    assert windowed and all(-1 in g.tables["r"] for g in windowed if g.spec.window < 200)       # pages were given back
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_greedy_generation_through_the_scheduler(folders, oracle, name):
+    """``Engine.generate`` (scheduler, portions of 16, sampler, steps queued ahead) gives the plain model's greedy
+    continuation."""
+    engine = _engine(folders, name, "float32", chunk=16, max_batch_tokens=48)
+    prompts = [_tokens(name, n, salt=40 + n) for n in (5, 37, 1, 70)]
+    outputs = engine.generate(prompts, n=12)
+    for prompt, produced in zip(prompts, outputs):
+        sequence = list(prompt)
+        for token in produced:
+            logits = oracle(name, "float32", sequence)[-1]
+            best = int(torch.argmax(logits))
+            if token != best:          # only a tie within rounding may differ
+                assert float(logits[best] - logits[token]) < 1e-4 * float(logits.abs().max()), (name, len(sequence))
+            sequence.append(int(token))
+        assert len(produced) == 12
+    assert not engine.cache.live_requests()
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_of_a_mozepel_model(folders, oracle, tmp_path, dtype):
+    """bin/trace_run as a subprocess: two requests, portions and single tokens in one batch, slots given back."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    a, b = _tokens("A", 60, salt=90), _tokens("A", 9, salt=91)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [0, 39]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[40:41], "want": [0]}, {"id": "b", "tokens": b[:7], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": b[7:], "want": [1]}, {"id": "a", "tokens": a[41:], "want": [18]}], "end": ["a", "b"]}]
+    out = tmp_path / "out"
+    run = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders["A"], "--dtype", dtype,
+                          "--out", str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                         capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert [line for line in run.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ref_a, ref_b = oracle("A", dtype, a), oracle("A", dtype, b)
+    want = {0: ref_a[[0, 39]], 1: ref_a[[40]], 2: torch.cat([ref_b[[8]], ref_a[[59]]])}
+    for step, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(ref.shape))
+        assert rel_error(got, ref) < MODEL_TOL[dtype]
+
+
+def test_command_line_serves_the_design(folders, capsys):
+    """`tge generate`, `tge bench decode / prefill / mixed` and `tge plan` with a Mozepel folder: the commands know no design."""
+    from aegean_tge_b200.cli import main
+    assert main(["generate", "--model", folders["D"], "--tokens", "5 17 3", "--n", "6", "--print-ids", "--context", "128"]) == 0
+    out = capsys.readouterr().out
+    assert "prefill  :" in out and "decode   :" in out and len(out.split("ids      :")[1].split()) == 6
+    common = ["--model", folders["D"], "--context", "512", "--max-requests", "12"]
+    assert main(["bench", "decode", *common, "--batch", "3", "--prompt-len", "40", "--n", "4"]) == 0
+    assert main(["bench", "prefill", *common, "--prompt-len", "100", "--repeat", "1"]) == 0
+    assert main(["plan", "--model", folders["A"], "--context", "256", "--sessions", "2"]) == 0
+    capsys.readouterr()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sampled_generation_with_requests_that_come_and_go(folders, dtype):
+    """Twelve requests with temperature, top-k and top-p samplers through six slots, then three, and a small pool:
+    all finish, the same seeds give the same tokens whatever shared a step with what (so no state leaks between the
+    slots' users, and steps queued ahead and dropped leave none), every page comes back."""
+    from aegean_tge_b200 import SamplingParams
+    prompts = [_tokens("A", 3 + 11 * i, salt=300 + i) for i in range(12)]
+    params = [SamplingParams(temperature=0.8, top_k=(0, 20, 50)[i % 3], top_p=(1.0, 0.9)[i % 2], seed=40 + i) for i in range(12)]
+    outputs = []
+    for slots, budget, chunk in ((6, 64, 16), (3, 256, 64)):
+        engine = _engine(folders, "A", dtype, max_requests=slots, max_batch_tokens=budget, chunk=chunk, max_tokens=640)
+        outputs.append(engine.generate(prompts, n=10, sampling=params))
+        assert all(len(row) == 10 for row in outputs[-1]) and not engine.cache.live_requests()
+        engine.cache.check()
+    if dtype == "float32":
+        assert outputs[0] == outputs[1]
