@@ -222,7 +222,30 @@ def paired_configs(width: int, heads: int, kv_heads: int, head_dim: int, gated_i
              "mlp": {"kind": "dense", "ff": gated_inner * 3 // 2}}
     lepizen = {"architecture": "Lepizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
                "logit_scale": 1.0, "logit_softcap": 50.0, "layers": [layer] * layers}
-    return {"qwen2": qwen2, "lepizen": lepizen}
+    return {"qwen2": qwen2, "lepizen": lepizen, "mozepel": mozepel_config(width, heads, kv_heads, head_dim, gated_inner, layers, vocab)}
+
+
+def mozepel_config(width: int, heads: int, kv_heads: int, head_dim: int, gated_inner: int, layers: int, vocab: int,
+                   window: int = 1024, pool: int = 64) -> dict:
+    """A Mozepel config.json with the width, heads, head size, inner width and layer count of a Qwen2 shape: three
+    retention layers (heads x head_dim keys and values) to one parallel layer (a window of ``window`` tokens with
+    blocks of ``pool``, four taps, half of each head rotated; beside it half as many decayed heads with keys of half
+    the size), all with the gated feed-forward."""
+    decay = lambda n: [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(n - 1, 1)) for h in range(n)]
+    mlp = {"kind": "dense", "ff": gated_inner}
+    retention = {"type": "retention", "mlp": mlp,
+                 "mixer": {"heads": heads, "dim": head_dim, "vdim": head_dim, "decay": decay(heads),
+                           "rot": {"base": 1000000.0, "dims": head_dim}}}
+    right_heads = max(heads // 2, 1)
+    parallel = {"type": "parallel", "mlp": mlp,
+                "mixer": {"left_scale": 1.0, "right_scale": 0.5,
+                          "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                                   "conv": 4, "mask": {"size": window, "pool": pool},
+                                   "rot": {"base": 500000.0, "dims": head_dim // 2,
+                                           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+                          "right": {"heads": right_heads, "dim": max(head_dim // 2, 1), "vdim": head_dim, "decay": decay(right_heads)}}}
+    return {"architecture": "Mozepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "layers": [parallel if n % 4 == 3 else retention for n in range(layers)]}
 
 
 def compare_designs(configs: Dict[str, dict], prompt_len: int = 2048, batches=(8, 64), steps: int = 32, warmup: int = 3,

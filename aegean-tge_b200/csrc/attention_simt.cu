@@ -132,7 +132,101 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
   }
 }
 
+// The pooled blocks alone, as a state for the tensor-core kernels' merge of key splits: for each (token, head) the
+// unnormalised sums over the pooled entries the query sees, acc = sum_b 2^(s_b - m) v_b, with m = max_b s_b and
+// l = sum_b 2^(s_b - m), scores in base-2 units (s = q . k * scale * log2 e).  No entry seen: (m, l) = (-inf, 0).
+template <typename T>
+__global__ void __launch_bounds__(128) attention_pooled_state_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ kp_pages, const T* __restrict__ vp_pages,
+    const int* __restrict__ pool_table, int pool_max_pages, int pool_num_pages, int page_size,
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, float* __restrict__ state_o,
+    float* __restrict__ state_ml, int heads, int kv_heads, int head_dim, int value_dim, float scale_log2, int window,
+    int pool, int* status) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * 4 + warp;
+  if (h >= heads) return;
+  const int kvh = h / (heads / kv_heads);
+  const int pos = positions[t];
+  const int seq = seq_of_token[t];
+  const int first = pos - window + 1 > 0 ? pos - window + 1 : 0;
+  const int seen = first / pool;
+  float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
+  const T* qrow = q + (size_t)t * q_stride + (size_t)h * head_dim;
+#pragma unroll
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    qv[i] = d < head_dim ? to_float<T>(qrow[d]) : 0.0f;
+    acc[i] = 0.0f;
+  }
+  float m = -INFINITY, l = 0.0f;
+  const int* ptable = pool_table + (size_t)seq * pool_max_pages;
+  for (int entry = 0; entry < seen; ++entry) {
+    const int page_index = entry / page_size;
+    const int page = page_index < pool_max_pages ? ptable[page_index] : -1;
+    if (page < 0 || page >= pool_num_pages) {
+      if (lane == 0) atomicOr(status, TGE_STATUS_BAD_PAGE);
+      break;
+    }
+    const T* krow = kp_pages + (((size_t)page * kv_heads + kvh) * page_size + entry % page_size) * head_dim;
+    const T* vrow = vp_pages + (((size_t)page * kv_heads + kvh) * page_size + entry % page_size) * value_dim;
+    float dot = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < head_dim) dot = fmaf(qv[i], to_float<T>(krow[d]), dot);
+    }
+    const float s = warp_sum(dot) * scale_log2;
+    const float m_new = fmaxf(m, s);
+    const float corr = exp2f(m - m_new);
+    const float w = exp2f(s - m_new);
+    l = l * corr + w;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < value_dim) acc[i] = fmaf(w, to_float<T>(vrow[d]), acc[i] * corr);
+    }
+    m = m_new;
+  }
+  const size_t slot = (size_t)t * heads + h;
+#pragma unroll
+  for (int i = 0; i < MAX_PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    if (d < value_dim) state_o[slot * value_dim + d] = acc[i];
+  }
+  if (lane == 0) {
+    state_ml[slot * 2] = m;
+    state_ml[slot * 2 + 1] = l;
+  }
+}
+
 }  // namespace
+
+TGE_API int tge_attention_pooled_state(const void* q, int q_stride, const void* kp_pages, const void* vp_pages,
+                                       const int* pool_table, int pool_max_pages, int pool_num_pages, int page_size,
+                                       const int* positions, const int* seq_of_token, float* state_o, float* state_ml,
+                                       int tokens, int heads, int kv_heads, int head_dim, int value_dim, float scale,
+                                       int window, int pool, int is_bf16, int* status, cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention: heads %d, kv heads %d", heads, kv_heads);
+  TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE && value_dim > 0 && value_dim <= 32 * MAX_PER_LANE,
+              "attention: head sizes %d and %d outside (0, %d]", head_dim, value_dim, 32 * MAX_PER_LANE);
+  TGE_REQUIRE(window > 0 && pool > 0 && page_size > 0 && pool_max_pages > 0 && pool_num_pages > 0,
+              "attention: pooled blocks need a window, their size and their pages");
+  if (tokens == 0) return 0;
+  dim3 grid(tokens, (heads + 3) / 4);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (is_bf16)
+    attention_pooled_state_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages, pool_table,
+        pool_max_pages, pool_num_pages, page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim,
+        value_dim, scale_log2, window, pool, status);
+  else
+    attention_pooled_state_kernel<float><<<grid, 128, 0, stream>>>(
+        (const float*)q, q_stride, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages,
+        page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim, value_dim, scale_log2, window, pool,
+        status);
+  return tge_launched("attention_pooled_state", 1);
+}
 
 TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_pages, int num_pages, int page_size,

@@ -12,6 +12,8 @@
 //
 // All statistics, states, angles and sums are float32 in both number formats; what is bfloat16 in the
 // bfloat16 path is the projections these kernels read and the rows they hand to the next product.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace {
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     int rotary, float k_scale, const float* __restrict__ decay, float* __restrict__ state,
     const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
     float* __restrict__ out, int* status) {
-  extern __shared__ float shared[];
+  extern __shared__ __align__(16) float shared[];
   float* qs = shared;                                   // [SCAN_TOKENS][dim]
   float* ks = qs + SCAN_TOKENS * dim;                   // [SCAN_TOKENS][dim]
   float* partial = ks + SCAN_TOKENS * dim;              // [SCAN_WARPS][SCAN_TOKENS][32]
@@ -157,6 +159,175 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
   for (int r = 0; r < ROWS; ++r) {
     const int i = warp * ROWS + r;
     if (live && i < dim) mine[(size_t)i * vdim] = s[r];
+  }
+}
+
+// The same recurrence for portions of many tokens, CHUNK tokens at a time.  With S the state before a chunk of n
+// tokens, c the head's decay and t, j places in the chunk:
+//   o_t   = c^(t+1) S^T q_t + sum_(j <= t) c^(t-j) (q_t . k_j) v_j
+//   S_new = c^n S + sum_j k_j (c^(n-1-j) v_j)^T
+// so a chunk is three small products on the CUDA cores (scores, readout, state update), all float32, instead of n
+// dependent steps.  Only non-negative powers of c occur, so a small decay loses nothing.  A block owns 32 columns of
+// one head's state for one request, as in the token-by-token kernel; the state stays in shared memory between
+// chunks.  A row's result differs from the token-by-token kernel's by rounding only.
+constexpr int CHUNK = 32;
+constexpr int CHUNK_THREADS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
+    const T* __restrict__ rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
+    int activation, const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
+    int rotary, float k_scale, const float* __restrict__ decay, float* __restrict__ state,
+    const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
+    float* __restrict__ out, int* status) {
+  extern __shared__ __align__(16) float shared[];
+  const int ldq = dim + 1;
+  float* Qs = shared;                         // [CHUNK][dim + 1]
+  float* Ks = Qs + CHUNK * ldq;               // [CHUNK][dim + 1]
+  float* Vs = Ks + CHUNK * ldq;               // [CHUNK][32]
+  float* Vd = Vs + CHUNK * 32;                // [CHUNK][32]   v_j * c^(n-1-j)
+  float* As = Vd + CHUNK * 32;                // [CHUNK (j)][CHUNK + 1 (t)]   c^(t-j) q_t . k_j
+  float* Ss = As + CHUNK * (CHUNK + 1);       // [dim][32]
+  float* pw = Ss + dim * 32;                  // c^0 .. c^CHUNK
+  const int tid = threadIdx.x;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int column0 = blockIdx.x * 32;
+  const int first = q_start[seq], last = q_start[seq + 1];
+  if (first >= last) return;
+  const int slot = slots[seq];
+  const float c = decay[head];
+  const int half = rotary >> 1;
+  float* mine = state + (((size_t)slot * heads + head) * dim) * vdim;
+  if (tid == 0) {
+    float power = 1.0f;
+    for (int m = 0; m <= CHUNK; ++m) { pw[m] = power; power *= c; }
+  }
+  for (int e = tid; e < dim * 32; e += CHUNK_THREADS) {
+    const int i = e >> 5, col = column0 + (e & 31);
+    Ss[e] = col < vdim ? mine[(size_t)i * vdim + col] : 0.0f;
+  }
+  const int t_of = tid >> 3, quad = (tid & 7) * 4;      // a thread's row (or row group) and its four columns
+  for (int base = first; base < last; base += CHUNK) {
+    const int n = min(CHUNK, last - base);
+    __syncthreads();                                     // the powers and the state are there; the last chunk is done with Ks, Vd
+    for (int e = tid; e < CHUNK * dim; e += CHUNK_THREADS) {
+      const int t = e / dim, i = e - t * dim;
+      float q = 0.0f, k = 0.0f;
+      if (t < n) {
+        const T* row = rows + (size_t)(base + t) * ld;
+        q = to_float<T>(row[q_off + head * dim + i]);
+        k = to_float<T>(row[k_off + head * dim + i]);
+        if (activation) { q = silu_f(q); k = silu_f(k); }
+        if (i < rotary) {
+          const int other = i < half ? i + half : i - half;
+          float q2 = to_float<T>(row[q_off + head * dim + other]);
+          float k2 = to_float<T>(row[k_off + head * dim + other]);
+          if (activation) { q2 = silu_f(q2); k2 = silu_f(k2); }
+          int position = positions[base + t];
+          if (position < 0 || position >= table_positions) {
+            atomicOr(status, TGE_STATUS_BAD_ROW);
+            position = 0;
+          }
+          const float cs = cos_table[(size_t)position * half + (i < half ? i : i - half)];
+          const float sn = sin_table[(size_t)position * half + (i < half ? i : i - half)];
+          q = i < half ? q * cs - q2 * sn : q * cs + q2 * sn;
+          k = i < half ? k * cs - k2 * sn : k * cs + k2 * sn;
+        }
+        k *= k_scale;
+      }
+      Qs[t * ldq + i] = q;
+      Ks[t * ldq + i] = k;
+    }
+    for (int e = tid; e < CHUNK * 32; e += CHUNK_THREADS) {
+      const int t = e >> 5, col = column0 + (e & 31);
+      float v = 0.0f;
+      if (t < n && col < vdim) {
+        v = to_float<T>(rows[(size_t)(base + t) * ld + v_off + head * vdim + col]);
+        if (activation) v = silu_f(v);
+      }
+      Vs[e] = v;
+      Vd[e] = t < n ? v * pw[n - 1 - t] : 0.0f;
+    }
+    __syncthreads();
+    // scores of the chunk, decayed: row t, columns quad .. quad + 3, at or below the diagonal
+    if (quad <= t_of) {
+      float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+      const float* qrow = Qs + t_of * ldq;
+      const float* krow = Ks + quad * ldq;
+      for (int i = 0; i < dim; ++i) {
+        const float q = qrow[i];
+        a0 = fmaf(q, krow[i], a0);
+        a1 = fmaf(q, krow[ldq + i], a1);
+        a2 = fmaf(q, krow[2 * ldq + i], a2);
+        a3 = fmaf(q, krow[3 * ldq + i], a3);
+      }
+      if (quad <= t_of) As[quad * (CHUNK + 1) + t_of] = a0 * pw[t_of - quad];
+      if (quad + 1 <= t_of) As[(quad + 1) * (CHUNK + 1) + t_of] = a1 * pw[t_of - quad - 1];
+      if (quad + 2 <= t_of) As[(quad + 2) * (CHUNK + 1) + t_of] = a2 * pw[t_of - quad - 2];
+      if (quad + 3 <= t_of) As[(quad + 3) * (CHUNK + 1) + t_of] = a3 * pw[t_of - quad - 3];
+    }
+    __syncthreads();
+    // readout: row t, four of the block's columns
+    {
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+      const float* qrow = Qs + t_of * ldq;
+      for (int i = 0; i < dim; ++i) {
+        const float q = qrow[i];
+        const float4 s4 = *reinterpret_cast<const float4*>(Ss + i * 32 + quad);
+        o0 = fmaf(q, s4.x, o0); o1 = fmaf(q, s4.y, o1); o2 = fmaf(q, s4.z, o2); o3 = fmaf(q, s4.w, o3);
+      }
+      const float carried = pw[t_of + 1];
+      o0 *= carried; o1 *= carried; o2 *= carried; o3 *= carried;
+      for (int j = 0; j <= t_of; ++j) {
+        const float a = As[j * (CHUNK + 1) + t_of];
+        const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * 32 + quad);
+        o0 = fmaf(a, v4.x, o0); o1 = fmaf(a, v4.y, o1); o2 = fmaf(a, v4.z, o2); o3 = fmaf(a, v4.w, o3);
+      }
+      if (t_of < n) {
+        float* dst = out + (size_t)(base + t_of) * heads * vdim + (size_t)head * vdim + column0 + quad;
+        const int room = vdim - column0 - quad;
+        if (room > 0) dst[0] = o0;
+        if (room > 1) dst[1] = o1;
+        if (room > 2) dst[2] = o2;
+        if (room > 3) dst[3] = o3;
+      }
+    }
+    __syncthreads();
+    // state: rows t_of, t_of + 32, ... of the block's four columns
+    {
+      float acc[8][4];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+      for (int j = 0; j < n; ++j) {
+        const float4 v4 = *reinterpret_cast<const float4*>(Vd + j * 32 + quad);
+        const float* krow = Ks + j * ldq + t_of;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (t_of + 32 * r < dim) {
+            const float k = krow[32 * r];
+            acc[r][0] = fmaf(k, v4.x, acc[r][0]); acc[r][1] = fmaf(k, v4.y, acc[r][1]);
+            acc[r][2] = fmaf(k, v4.z, acc[r][2]); acc[r][3] = fmaf(k, v4.w, acc[r][3]);
+          }
+        }
+      }
+      const float kept = pw[n];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const int i = t_of + 32 * r;
+        if (i < dim) {
+          float4* cell = reinterpret_cast<float4*>(Ss + i * 32 + quad);
+          float4 s4 = *cell;
+          s4.x = fmaf(kept, s4.x, acc[r][0]); s4.y = fmaf(kept, s4.y, acc[r][1]);
+          s4.z = fmaf(kept, s4.z, acc[r][2]); s4.w = fmaf(kept, s4.w, acc[r][3]);
+          *cell = s4;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < dim * 32; e += CHUNK_THREADS) {
+    const int i = e >> 5, col = column0 + (e & 31);
+    if (col < vdim) mine[(size_t)i * vdim + col] = Ss[e];
   }
 }
 
@@ -364,8 +535,27 @@ template <typename T>
 int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
                       int activation, const float* cos_table, const float* sin_table, int table_positions, int rotary,
                       float k_scale, const float* decay, float* state, const int* slots, const int* q_start,
-                      const int* positions, float* out, int num_seqs, int* status, cudaStream_t stream) {
+                      const int* positions, float* out, int num_seqs, int max_q_len, int* status, cudaStream_t stream) {
   dim3 grid((vdim + 31) / 32, heads, num_seqs);
+  // portions of some length go chunk by chunk; single tokens and short portions token by token
+  const size_t chunked = (size_t)(2 * CHUNK * (dim + 1) + 2 * CHUNK * 32 + CHUNK * (CHUNK + 1) + dim * 32 + CHUNK + 1 + 3) * sizeof(float);
+  static const bool chunks_ok = getenv("TGE_NO_CHUNKED_SCAN") == nullptr || getenv("TGE_NO_CHUNKED_SCAN")[0] == '\0';
+  if (chunks_ok && max_q_len >= CHUNK / 2 && dim <= 256 && chunked <= 200 * 1024) {
+    static size_t configured[2] = {0, 0};
+    const int which = sizeof(T) == 2 ? 1 : 0;
+    if (chunked > 48 * 1024 && chunked > configured[which]) {
+      cudaError_t err = cudaFuncSetAttribute(decay_scan_chunked_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)chunked);
+      if (err != cudaSuccess) {
+        tge_set_error("decay_scan: cannot reserve %zu bytes of shared memory: %s", chunked, cudaGetErrorString(err));
+        return -2;
+      }
+      configured[which] = chunked;
+    }
+    decay_scan_chunked_kernel<T><<<grid, CHUNK_THREADS, chunked, stream>>>(
+        (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table, table_positions, rotary,
+        k_scale, decay, state, slots, q_start, positions, out, status);
+    return tge_launched("decay_scan_chunked", 1);
+  }
   const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_WARPS * SCAN_TOKENS * 32) * sizeof(float);
   const int per_warp = (dim + SCAN_WARPS - 1) / SCAN_WARPS;
 #define TGE_SCAN(ROWS)                                                                                            \
@@ -407,7 +597,7 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
                            int dim, int vdim, int activation, const float* cos_table, const float* sin_table,
                            int table_positions, int rotary, float k_scale, const float* decay, float* state,
                            const int* slots, const int* q_start, const int* positions, float* out, int num_seqs,
-                           int tokens, int* status, cudaStream_t stream) {
+                           int tokens, int max_q_len, int* status, cudaStream_t stream) {
   TGE_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && dim <= 64 * SCAN_WARPS, "decay_scan: %d heads of %d x %d (keys up to %d)",
               heads, dim, vdim, 64 * SCAN_WARPS);
   TGE_REQUIRE(rotary >= 0 && rotary % 2 == 0 && rotary <= dim, "decay_scan: %d rotated elements of %d", rotary, dim);
@@ -418,10 +608,10 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
   if (is_bf16)
     return launch_decay_scan<__nv_bfloat16>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table,
                                             sin_table, table_positions, rotary, k_scale, decay, state, slots, q_start,
-                                            positions, out, num_seqs, status, stream);
+                                            positions, out, num_seqs, max_q_len, status, stream);
   return launch_decay_scan<float>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,
                                   table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, num_seqs,
-                                  status, stream);
+                                  max_q_len, status, stream);
 }
 
 TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long long ld_gate, const float* weight, void* out,

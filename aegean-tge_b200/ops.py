@@ -94,12 +94,15 @@ def core() -> ctypes.CDLL:
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                                              _c_ptr, _c_ptr])
+        _declare(lib, "tge_attention_pooled_state", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                                                     _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                     _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_to_run_dtype", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
         _declare(lib, "tge_scale_add_norm", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float,
                                              _c_float, _c_ptr])
         _declare(lib, "tge_decay_scan", [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                          _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                                         _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr])
+                                         _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
         _declare(lib, "tge_gated_norm", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
                                          _c_float, _c_int, _c_ptr])
         _declare(lib, "tge_conv_norm_rope_store", [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
@@ -137,7 +140,7 @@ def attention_lib(head_dim: int, value_dim: int = 0) -> ctypes.CDLL:
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
                                             _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
-                                            _c_ptr])
+                                            _c_ptr, _c_ptr, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim or lib.tge_attention_mma_value_dim() != value_dim:
@@ -761,12 +764,34 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
             raise KernelError(f"pooled pages must be shaped like the keys' and values', got {tuple(pooled_k.shape)} "
                               f"and {tuple(pooled_v.shape)}")
         pool_pages, pool_width = pooled_k.shape[0], pool_table.shape[1]
-    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok and not pool
+    use_mma = (q.dtype == torch.bfloat16 and USE_MMA_ATTENTION and not force_simt and pairs_ok
                and mma_attention_supports(head_dim, heads, kv_heads, page_size, value_dim))
     if use_mma:
         lib = attention_lib(head_dim, value_dim)
-        prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 else 0
+        prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 and not pool else 0
         prefix_split = split_tokens
+        extra_o = extra_ml = None
+        if pool:
+            # The window's tokens go through the tensor-core kernels with their keys cut into at least two runs, so
+            # that they leave unnormalised states; the few pooled entries a query sees become one more state, from a
+            # kernel of their own, and the merge of the runs takes it in.
+            extra_o = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=q.device)
+            extra_ml = torch.empty((tokens, heads, 2), dtype=torch.float32, device=q.device)
+            core_lib = core()
+            _check(core_lib.tge_attention_pooled_state(q.data_ptr(), q_stride, pooled_k.data_ptr(), pooled_v.data_ptr(),
+                                                       pool_table.data_ptr(), pool_width, pool_pages, page_size,
+                                                       positions.data_ptr(), seq_of_token.data_ptr(), extra_o.data_ptr(),
+                                                       extra_ml.data_ptr(), tokens, heads, kv_heads, head_dim, value_dim,
+                                                       float(scale), window, int(pool), 1, status_word().data_ptr(),
+                                                       _stream()), core_lib)
+            if split_tokens == 0:
+                split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len, heads,
+                                                      kv_heads, bound=max_ctx_len)
+            if split_tokens == 0 or split_tokens >= max_ctx_len:
+                # one run would be normalised at once: cut in two (a bound of two tiles at least; a run beyond a
+                # request's keys holds nothing and is dropped by the merge)
+                max_ctx_len = max(max_ctx_len, 128)
+                split_tokens = 64 * -(-max_ctx_len // 128)
         if split_tokens == 0:
             split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len,
                                                   heads, kv_heads, bound=max_ctx_len)
@@ -783,7 +808,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
                                      split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
-                                     _ptr(sink), _stream()), lib)
+                                     _ptr(sink), _ptr(extra_o), _ptr(extra_ml), _stream()), lib)
         return out
     lib = core()
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
@@ -827,7 +852,8 @@ def scale_add_norm(x: torch.Tensor, y: torch.Tensor, alpha: float, weight: torch
 def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, dim: int, vdim: int,
                decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, q_start: torch.Tensor,
                positions: torch.Tensor, num_seqs: int, activation: bool = False, cos: Optional[torch.Tensor] = None,
-               sin: Optional[torch.Tensor] = None, rotary: int = 0, k_scale: float = 1.0) -> torch.Tensor:
+               sin: Optional[torch.Tensor] = None, rotary: int = 0, k_scale: float = 1.0,
+               max_q_len: int = 0) -> torch.Tensor:
     """Linear attention with a fixed decay per head over a flat batch of portions, its state carried per request.
 
     ``rows`` [T, ...] (run dtype, dense rows) holds the projections: q at column ``q_off`` and k at ``k_off``
@@ -835,7 +861,8 @@ def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: in
     k are rotated over their first ``rotary`` elements (tables float32 [positions, rotary/2]); k is multiplied by
     ``k_scale``.  Per head S <- decay S + k v^T and o = S^T q, token by token in float32; ``state`` is float32
     [slots, heads, dim, vdim], read and written in the row ``slots[s]`` of each portion.  Returns o, float32
-    [T, heads*vdim]."""
+    [T, heads*vdim].  ``max_q_len``: the longest portion (0: unknown, taken as long); steps with portions of 16 tokens
+    or more go chunk by chunk (three small products per 32 tokens), the others token by token."""
     _want(rows, "projections", _FLOAT, contiguous=False)
     ld = _rows_2d(rows, "projections")
     tokens = rows.shape[0]
@@ -861,7 +888,7 @@ def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: in
                               vdim, int(activation), _ptr(cos) if rotary else None, _ptr(sin) if rotary else None,
                               table_positions, rotary, float(k_scale), decay.data_ptr(), state.data_ptr(),
                               slots.data_ptr(), q_start.data_ptr(), positions.data_ptr(), out.data_ptr(), num_seqs, tokens,
-                              status_word().data_ptr(), _stream()), lib)
+                              int(max_q_len) if max_q_len > 0 else tokens, status_word().data_ptr(), _stream()), lib)
     return out
 
 

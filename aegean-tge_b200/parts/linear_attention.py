@@ -96,7 +96,7 @@ class DecayLinearAttention(Mixer):
         o = ops.decay_scan(rows, 0, self.q_dim, 2 * self.q_dim, self.heads, self.head_dim, self.value_dim, self.decay,
                            cache.state["state"], ctx.slots, ctx.q_start, ctx.positions, ctx.num_seqs,
                            activation=self.activation == "silu", cos=self.cos, sin=self.sin, rotary=self.rotary,
-                           k_scale=self.k_scale)
+                           k_scale=self.k_scale, max_q_len=ctx.max_q_len)
         gate = rows[:, 2 * self.q_dim + self.o_dim:]
         return ops.gated_norm(o, gate, self.norm_w, self.heads if self.out_norm == "head" else 1, self.eps,
                               sigmoid=self.gate == "sigmoid", out=out)

@@ -211,9 +211,11 @@ def test_frequencies_rescaled_by_wavelength():
 @pytest.mark.parametrize("heads,dim,vdim,rotary,activation,k_scale", [
     (3, 16, 48, 8, False, 0.25), (2, 32, 32, 32, False, 32 ** -0.5), (5, 12, 20, 0, True, 1.0), (2, 128, 64, 0, True, 1.0),
     (2, 64, 128, 64, False, 0.125), (1, 200, 70, 100, True, 0.5)])
-@pytest.mark.parametrize("cuts", [[[77]], [[40], [1], [1], [2], [33]], [[9, 1, 30], [8, 1, 30], [1, 1, 1]]])
-def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rotary, activation, k_scale, cuts):
-    """Requests cut into portions, each step a batch; the state lives in slots that are not in order."""
+@pytest.mark.parametrize("cuts", [[[77]], [[40], [1], [1], [2], [33]], [[9, 1, 30], [8, 1, 30], [1, 1, 1]], [[100, 3], [31, 64], [33, 17]]])
+@pytest.mark.parametrize("route", ["chunks", "tokens"])
+def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rotary, activation, k_scale, cuts, route):
+    """Requests cut into portions, each step a batch; the state lives in slots that are not in order.  Steps with a
+    portion of some length go chunk by chunk (``route`` "chunks"), or every step token by token."""
     from aegean_tge_b200.parts.rope import rotary_tables
     gen = torch.Generator().manual_seed(heads * 1000 + dim)
     count = len(cuts[0])
@@ -236,7 +238,8 @@ def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rot
         positions, _seq, q_start = _steps(step, done)
         out = ops.decay_scan(rows, 3, 3 + heads * dim, 5 + 2 * heads * dim, heads, dim, vdim,
                              torch.tensor(decay, dtype=torch.float32, device=DEV), state, _i32(slots), q_start, positions, count,
-                             activation=activation, cos=cos, sin=sin, rotary=rotary, k_scale=k_scale)
+                             activation=activation, cos=cos, sin=sin, rotary=rotary, k_scale=k_scale,
+                             max_q_len=max(step) if route == "chunks" else 1)
         at = 0
         for s in range(count):
             got[s].append(out[at:at + step[s]])
