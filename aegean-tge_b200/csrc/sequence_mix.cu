@@ -50,6 +50,59 @@ __global__ void __launch_bounds__(256) scale_add_norm_kernel(float* __restrict__
   }
 }
 
+// The same with 16-byte accesses and the row held in registers between the two passes: rows of a multiple of four
+// elements, at most sixteen per thread.
+__device__ __forceinline__ void store_quad(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store_quad(__nv_bfloat16* dst, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024) scale_add_norm_vec_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                                  long long ldy, const float* __restrict__ weight,
+                                                                  T* __restrict__ copy, int hidden, float alpha, float eps) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  const int quads = hidden >> 2;
+  float4 gain[4], value[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {                  // constants of the model: before the wait
+    const int i = threadIdx.x + k * blockDim.x;
+    gain[k] = i < quads ? reinterpret_cast<const float4*>(weight)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  float4* row = reinterpret_cast<float4*>(x + (size_t)blockIdx.x * hidden);
+  const float4* add = reinterpret_cast<const float4*>(y + (size_t)blockIdx.x * ldy);
+  float sum = 0.0f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < quads) {
+      const float4 a = row[i], b = add[i];
+      v = make_float4(fmaf(alpha, a.x, b.x), fmaf(alpha, a.y, b.y), fmaf(alpha, a.z, b.z), fmaf(alpha, a.w, b.w));
+    }
+    value[k] = v;
+    sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum); sum = fmaf(v.z, v.z, sum); sum = fmaf(v.w, v.w, sum);
+  }
+  sum = block_sum(sum, scratch);
+  const float scale = 1.0f / sqrtf(sum / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < quads) {
+      const float4 v = make_float4(value[k].x * scale * gain[k].x, value[k].y * scale * gain[k].y,
+                                   value[k].z * scale * gain[k].z, value[k].w * scale * gain[k].w);
+      row[i] = v;
+      if (copy != nullptr) store_quad(copy + (size_t)blockIdx.x * hidden + 4 * (size_t)i, v);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Linear attention with a decay per head.  A block owns 32 columns of one head's state for one request and walks
 // the request's tokens of this step in order, SCAN_TOKENS at a time: the block prepares their q and k (activation,
@@ -60,7 +113,7 @@ __global__ void __launch_bounds__(256) scale_add_norm_kernel(float* __restrict__
 constexpr int SCAN_TOKENS = 8;
 constexpr int SCAN_WARPS = 4;
 
-template <typename T, int ROWS>
+template <typename T, int ROWS, int TOKENS>
 __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     const T* __restrict__ rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
     int activation, const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
@@ -68,9 +121,9 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
     float* __restrict__ out, int* status) {
   extern __shared__ __align__(16) float shared[];
-  float* qs = shared;                                   // [SCAN_TOKENS][dim]
-  float* ks = qs + SCAN_TOKENS * dim;                   // [SCAN_TOKENS][dim]
-  float* partial = ks + SCAN_TOKENS * dim;              // [SCAN_WARPS][SCAN_TOKENS][32]
+  float* qs = shared;                                   // [TOKENS][dim]
+  float* ks = qs + TOKENS * dim;                   // [TOKENS][dim]
+  float* partial = ks + TOKENS * dim;              // [SCAN_WARPS][TOKENS][32]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int head = blockIdx.y, seq = blockIdx.z;
   const int column = blockIdx.x * 32 + lane;
@@ -87,8 +140,8 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     const int i = warp * ROWS + r;
     s[r] = (live && i < dim) ? mine[(size_t)i * vdim] : 0.0f;
   }
-  for (int base = first; base < last; base += SCAN_TOKENS) {
-    const int count = min(SCAN_TOKENS, last - base);
+  for (int base = first; base < last; base += TOKENS) {
+    const int count = min(TOKENS, last - base);
     // q and k of these tokens as the recurrence takes them
     for (int e = threadIdx.x; e < count * dim; e += blockDim.x) {
       const int n = e / dim, i = e - n * dim;
@@ -115,9 +168,9 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
       qs[e] = q;
       ks[e] = k * k_scale;
     }
-    float v[SCAN_TOKENS];
+    float v[TOKENS];
 #pragma unroll
-    for (int n = 0; n < SCAN_TOKENS; ++n) {
+    for (int n = 0; n < TOKENS; ++n) {
       float value = 0.0f;
       if (live && n < count) {
         value = to_float<T>(rows[(size_t)(base + n) * ld + v_off + head * vdim + column]);
@@ -127,7 +180,7 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     }
     __syncthreads();
 #pragma unroll
-    for (int n = 0; n < SCAN_TOKENS; ++n) {
+    for (int n = 0; n < TOKENS; ++n) {
       float acc = 0.0f;
       if (n < count) {
         const float* qn = qs + n * dim + warp * ROWS;
@@ -140,14 +193,14 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
           }
         }
       }
-      partial[(warp * SCAN_TOKENS + n) * 32 + lane] = acc;
+      partial[(warp * TOKENS + n) * 32 + lane] = acc;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < count * 32; e += blockDim.x) {
       const int n = e >> 5, l = e & 31;
       float total = 0.0f;
 #pragma unroll
-      for (int w = 0; w < SCAN_WARPS; ++w) total += partial[(w * SCAN_TOKENS + n) * 32 + l];
+      for (int w = 0; w < SCAN_WARPS; ++w) total += partial[(w * TOKENS + n) * 32 + l];
       const int col = blockIdx.x * 32 + l;
       if (col < vdim) out[(size_t)(base + n) * heads * vdim + head * vdim + col] = total;
     }
@@ -159,6 +212,42 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
   for (int r = 0; r < ROWS; ++r) {
     const int i = warp * ROWS + r;
     if (live && i < dim) mine[(size_t)i * vdim] = s[r];
+  }
+}
+
+// q and k as the recurrence takes them (activation, rotation, the factor on k), float32 [tokens, heads, 2, dim]: once
+// per step for the chunked kernels, whose blocks (one per run of state columns) would each redo it otherwise.
+template <typename T>
+__global__ void __launch_bounds__(128) decay_prepare_kernel(
+    const T* __restrict__ rows, long long ld, int q_off, int k_off, int heads, int dim, int activation,
+    const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions, int rotary,
+    float k_scale, const int* __restrict__ positions, float* __restrict__ prepared, int* status) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int half = rotary >> 1;
+  const T* row = rows + (size_t)t * ld;
+  int position = positions[t];
+  if (rotary > 0 && (position < 0 || position >= table_positions)) {
+    if (threadIdx.x == 0) atomicOr(status, TGE_STATUS_BAD_ROW);
+    position = 0;
+  }
+  float* dst = prepared + ((size_t)t * heads + head) * 2 * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float q = to_float<T>(row[q_off + head * dim + i]);
+    float k = to_float<T>(row[k_off + head * dim + i]);
+    if (activation) { q = silu_f(q); k = silu_f(k); }
+    if (i < rotary) {
+      const int other = i < half ? i + half : i - half;
+      float q2 = to_float<T>(row[q_off + head * dim + other]);
+      float k2 = to_float<T>(row[k_off + head * dim + other]);
+      if (activation) { q2 = silu_f(q2); k2 = silu_f(k2); }
+      const float cs = cos_table[(size_t)position * half + (i < half ? i : i - half)];
+      const float sn = sin_table[(size_t)position * half + (i < half ? i : i - half)];
+      // the pair (u, v) = (element i, element i + half) becomes (u cos - v sin, v cos + u sin)
+      q = i < half ? q * cs - q2 * sn : q * cs + q2 * sn;
+      k = i < half ? k * cs - k2 * sn : k * cs + k2 * sn;
+    }
+    dst[i] = q;
+    dst[dim + i] = k * k_scale;
   }
 }
 
@@ -175,11 +264,9 @@ constexpr int CHUNK_THREADS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
-    const T* __restrict__ rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
-    int activation, const float* __restrict__ cos_table, const float* __restrict__ sin_table, int table_positions,
-    int rotary, float k_scale, const float* __restrict__ decay, float* __restrict__ state,
-    const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
-    float* __restrict__ out, int* status) {
+    const T* __restrict__ rows, long long ld, const float* __restrict__ prepared, int v_off, int heads, int dim, int vdim,
+    int activation, const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ slots,
+    const int* __restrict__ q_start, float* __restrict__ out) {
   extern __shared__ __align__(16) float shared[];
   const int ldq = dim + 1;
   float* Qs = shared;                         // [CHUNK][dim + 1]
@@ -196,7 +283,6 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
   if (first >= last) return;
   const int slot = slots[seq];
   const float c = decay[head];
-  const int half = rotary >> 1;
   float* mine = state + (((size_t)slot * heads + head) * dim) * vdim;
   if (tid == 0) {
     float power = 1.0f;
@@ -214,26 +300,9 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
       const int t = e / dim, i = e - t * dim;
       float q = 0.0f, k = 0.0f;
       if (t < n) {
-        const T* row = rows + (size_t)(base + t) * ld;
-        q = to_float<T>(row[q_off + head * dim + i]);
-        k = to_float<T>(row[k_off + head * dim + i]);
-        if (activation) { q = silu_f(q); k = silu_f(k); }
-        if (i < rotary) {
-          const int other = i < half ? i + half : i - half;
-          float q2 = to_float<T>(row[q_off + head * dim + other]);
-          float k2 = to_float<T>(row[k_off + head * dim + other]);
-          if (activation) { q2 = silu_f(q2); k2 = silu_f(k2); }
-          int position = positions[base + t];
-          if (position < 0 || position >= table_positions) {
-            atomicOr(status, TGE_STATUS_BAD_ROW);
-            position = 0;
-          }
-          const float cs = cos_table[(size_t)position * half + (i < half ? i : i - half)];
-          const float sn = sin_table[(size_t)position * half + (i < half ? i : i - half)];
-          q = i < half ? q * cs - q2 * sn : q * cs + q2 * sn;
-          k = i < half ? k * cs - k2 * sn : k * cs + k2 * sn;
-        }
-        k *= k_scale;
+        const float* src = prepared + ((size_t)(base + t) * heads + head) * 2 * dim;
+        q = src[i];
+        k = src[dim + i];
       }
       Qs[t * ldq + i] = q;
       Ks[t * ldq + i] = k;
@@ -254,6 +323,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
       float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
       const float* qrow = Qs + t_of * ldq;
       const float* krow = Ks + quad * ldq;
+#pragma unroll 8
       for (int i = 0; i < dim; ++i) {
         const float q = qrow[i];
         a0 = fmaf(q, krow[i], a0);
@@ -271,6 +341,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
     {
       float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
       const float* qrow = Qs + t_of * ldq;
+#pragma unroll 8
       for (int i = 0; i < dim; ++i) {
         const float q = qrow[i];
         const float4 s4 = *reinterpret_cast<const float4*>(Ss + i * 32 + quad);
@@ -278,6 +349,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
       }
       const float carried = pw[t_of + 1];
       o0 *= carried; o1 *= carried; o2 *= carried; o3 *= carried;
+#pragma unroll 4
       for (int j = 0; j <= t_of; ++j) {
         const float a = As[j * (CHUNK + 1) + t_of];
         const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * 32 + quad);
@@ -298,6 +370,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
       float acc[8][4];
 #pragma unroll
       for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+#pragma unroll 2
       for (int j = 0; j < n; ++j) {
         const float4 v4 = *reinterpret_cast<const float4*>(Vd + j * 32 + quad);
         const float* krow = Ks + j * ldq + t_of;
@@ -327,6 +400,199 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
   __syncthreads();
   for (int e = tid; e < dim * 32; e += CHUNK_THREADS) {
     const int i = e >> 5, col = column0 + (e & 31);
+    if (col < vdim) mine[(size_t)i * vdim + col] = Ss[e];
+  }
+}
+
+// The chunked kernel for keys of up to 128 elements: chunks of 64 tokens, 64 columns of the state per block, and
+// every thread a 4 x 4 (state: 8 x 4) tile of each product's result, so that a pair of 16-byte reads from shared
+// memory feeds sixteen multiply-adds.  q and k are kept transposed ([element][token]) for that.
+constexpr int WIDE = 64;                 // tokens per chunk and columns per block
+constexpr int WIDE_LD = WIDE + 4;        // row stride of the transposed tiles: 16-byte aligned
+
+__device__ __forceinline__ void copy16_async(float* dst_shared, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src));
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) decay_scan_wide_kernel(
+    const T* __restrict__ rows, long long ld, const float* __restrict__ prepared, int v_off, int heads, int dim, int vdim,
+    int activation, const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ slots,
+    const int* __restrict__ q_start, float* __restrict__ out) {
+  extern __shared__ __align__(16) float shared[];
+  float* Qt = shared;                         // [dim][WIDE_LD]   q, element-major
+  float* Kt = Qt + dim * WIDE_LD;             // [dim][WIDE_LD]   k, element-major
+  float* Vs = Kt + dim * WIDE_LD;             // [WIDE][WIDE]
+  float* Vd = Vs + WIDE * WIDE;               // [WIDE][WIDE]     v_j * c^(n-1-j)
+  float* As = Vd + WIDE * WIDE;               // [WIDE (j)][WIDE_LD (t)]   c^(t-j) q_t . k_j
+  float* Ss = As + WIDE * WIDE_LD;            // [dim][WIDE]
+  float* pw = Ss + dim * WIDE;                // c^0 .. c^WIDE
+  float* stage = pw + WIDE + 4;               // [WIDE][2 dim]: the next chunk's q and k on their way in (dim % 4 == 0)
+  const int tid = threadIdx.x;
+  const int head = blockIdx.y, seq = blockIdx.z;
+  const int column0 = blockIdx.x * WIDE;
+  const int first = q_start[seq], last = q_start[seq + 1];
+  if (first >= last) return;
+  const int slot = slots[seq];
+  const float c = decay[head];
+  float* mine = state + (((size_t)slot * heads + head) * dim) * vdim;
+  // A chunk's q and k (prepared rows, 2 dim floats per token and head) are copied asynchronously into `stage` while
+  // the chunk before is worked on, and its values wait in registers: the products never wait for memory.
+  const int quads_per_token = dim >> 1;       // 16-byte pieces of a row of 2 dim floats
+  auto fetch_qk = [&](int from) {
+    const int count = min(WIDE, last - from);
+    for (int e = tid; e < count * quads_per_token; e += 256) {
+      const int t = e / quads_per_token, piece = e - t * quads_per_token;
+      copy16_async(stage + (size_t)t * 2 * dim + 4 * piece, prepared + ((size_t)(from + t) * heads + head) * 2 * dim + 4 * piece);
+    }
+    copies_commit();
+  };
+  float ahead[16];                            // the next chunk's values for this thread's places in Vs
+  auto fetch_v = [&](int from) {
+    const int count = min(WIDE, last - from);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int e = tid + 256 * k;
+      const int t = e >> 6, col = column0 + (e & 63);
+      ahead[k] = (t < count && col < vdim) ? to_float<T>(rows[(size_t)(from + t) * ld + v_off + head * vdim + col]) : 0.0f;
+    }
+  };
+  fetch_qk(first);
+  fetch_v(first);
+  if (tid == 0) {
+    float power = 1.0f;
+    for (int m = 0; m <= WIDE; ++m) { pw[m] = power; power *= c; }
+  }
+  for (int e = tid; e < dim * WIDE; e += 256) {
+    const int i = e >> 6, col = column0 + (e & 63);
+    Ss[e] = col < vdim ? mine[(size_t)i * vdim + col] : 0.0f;
+  }
+  const int ty = tid >> 4, tx = tid & 15;
+  const int t0 = ty * 4, c0 = tx * 4;                    // a thread's four rows (tokens) and four columns
+  for (int base = first; base < last; base += WIDE) {
+    const int n = min(WIDE, last - base);
+    copies_wait();
+    __syncthreads();                                     // the copies, the powers and the state are there; the last chunk is done with Kt, Vd
+    for (int e = tid; e < WIDE * dim; e += 256) {
+      const int t = e / dim, i = e - t * dim;
+      const bool live = t < n;
+      Qt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + i] : 0.0f;
+      Kt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + dim + i] : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int e = tid + 256 * k;
+      const int t = e >> 6;
+      const float v = activation ? silu_f(ahead[k]) : ahead[k];
+      Vs[e] = t < n ? v : 0.0f;
+      Vd[e] = t < n ? v * pw[n - 1 - t] : 0.0f;
+    }
+    __syncthreads();
+    if (base + WIDE < last) {
+      fetch_qk(base + WIDE);
+      fetch_v(base + WIDE);
+    }
+    // scores of the chunk, decayed: tokens t0 .. t0 + 3 against keys c0 .. c0 + 3, tiles at or below the diagonal
+    if (c0 <= t0) {
+      float acc[4][4] = {};
+#pragma unroll 4
+      for (int i = 0; i < dim; ++i) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Qt + i * WIDE_LD + t0);
+        const float4 k4 = *reinterpret_cast<const float4*>(Kt + i * WIDE_LD + c0);
+        const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, kb[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const int j = c0 + b;
+        float4 cell;
+        cell.x = j <= t0 ? acc[0][b] * pw[t0 - j] : 0.0f;
+        cell.y = j <= t0 + 1 ? acc[1][b] * pw[t0 + 1 - j] : 0.0f;
+        cell.z = j <= t0 + 2 ? acc[2][b] * pw[t0 + 2 - j] : 0.0f;
+        cell.w = j <= t0 + 3 ? acc[3][b] * pw[t0 + 3 - j] : 0.0f;
+        *reinterpret_cast<float4*>(As + j * WIDE_LD + t0) = cell;
+      }
+    }
+    __syncthreads();
+    // readout: tokens t0 .. t0 + 3, columns c0 .. c0 + 3 of the block
+    {
+      float acc[4][4] = {};
+#pragma unroll 4
+      for (int i = 0; i < dim; ++i) {
+        const float4 q4 = *reinterpret_cast<const float4*>(Qt + i * WIDE_LD + t0);
+        const float4 s4 = *reinterpret_cast<const float4*>(Ss + i * WIDE + c0);
+        const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, sb[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], sb[b], acc[a][b]);
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const float carried = pw[t0 + a + 1];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] *= carried;
+      }
+      const int reach = min(t0 + 3, n - 1);
+#pragma unroll 4
+      for (int j = 0; j <= reach; ++j) {
+        const float4 a4 = *reinterpret_cast<const float4*>(As + j * WIDE_LD + t0);
+        const float4 v4 = *reinterpret_cast<const float4*>(Vs + j * WIDE + c0);
+        const float aa[4] = {a4.x, a4.y, a4.z, a4.w}, vb[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(aa[a], vb[b], acc[a][b]);
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        if (t0 + a < n) {
+          float* dst = out + (size_t)(base + t0 + a) * heads * vdim + (size_t)head * vdim + column0 + c0;
+          const int room = vdim - column0 - c0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (b < room) dst[b] = acc[a][b];
+        }
+      }
+    }
+    __syncthreads();
+    // state: rows 8 ty .. 8 ty + 7, columns c0 .. c0 + 3
+    {
+      float acc[8][4] = {};
+      const int i0 = ty * 8;
+#pragma unroll 2
+      for (int j = 0; j < n; ++j) {
+        const float4 v4 = *reinterpret_cast<const float4*>(Vd + j * WIDE + c0);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (i0 + r < dim) {
+            const float k = Kt[(i0 + r) * WIDE_LD + j];
+            acc[r][0] = fmaf(k, v4.x, acc[r][0]); acc[r][1] = fmaf(k, v4.y, acc[r][1]);
+            acc[r][2] = fmaf(k, v4.z, acc[r][2]); acc[r][3] = fmaf(k, v4.w, acc[r][3]);
+          }
+        }
+      }
+      const float kept = pw[n];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (i0 + r < dim) {
+          float4* cell = reinterpret_cast<float4*>(Ss + (i0 + r) * WIDE + c0);
+          float4 s4 = *cell;
+          s4.x = fmaf(kept, s4.x, acc[r][0]); s4.y = fmaf(kept, s4.y, acc[r][1]);
+          s4.z = fmaf(kept, s4.z, acc[r][2]); s4.w = fmaf(kept, s4.w, acc[r][3]);
+          *cell = s4;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < dim * WIDE; e += 256) {
+    const int i = e >> 6, col = column0 + (e & 63);
     if (col < vdim) mine[(size_t)i * vdim + col] = Ss[e];
   }
 }
@@ -535,12 +801,33 @@ template <typename T>
 int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
                       int activation, const float* cos_table, const float* sin_table, int table_positions, int rotary,
                       float k_scale, const float* decay, float* state, const int* slots, const int* q_start,
-                      const int* positions, float* out, int num_seqs, int max_q_len, int* status, cudaStream_t stream) {
+                      const int* positions, float* out, int num_seqs, int tokens, int max_q_len, float* prepared, int* status,
+                      cudaStream_t stream) {
   dim3 grid((vdim + 31) / 32, heads, num_seqs);
   // portions of some length go chunk by chunk; single tokens and short portions token by token
   const size_t chunked = (size_t)(2 * CHUNK * (dim + 1) + 2 * CHUNK * 32 + CHUNK * (CHUNK + 1) + dim * 32 + CHUNK + 1 + 3) * sizeof(float);
   static const bool chunks_ok = getenv("TGE_NO_CHUNKED_SCAN") == nullptr || getenv("TGE_NO_CHUNKED_SCAN")[0] == '\0';
-  if (chunks_ok && max_q_len >= CHUNK / 2 && dim <= 256 && chunked <= 200 * 1024) {
+  const size_t wide = (size_t)(2 * dim * WIDE_LD + 2 * WIDE * WIDE + WIDE * WIDE_LD + dim * WIDE + WIDE + 4 + WIDE * 2 * dim) * sizeof(float);
+  if (chunks_ok && prepared != nullptr && max_q_len >= WIDE && dim <= 128 && dim % 4 == 0 && wide <= 227 * 1024) {
+    static size_t configured[2] = {0, 0};
+    const int which = sizeof(T) == 2 ? 1 : 0;
+    if (wide > configured[which]) {
+      cudaError_t err = cudaFuncSetAttribute(decay_scan_wide_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide);
+      if (err != cudaSuccess) {
+        tge_set_error("decay_scan: cannot reserve %zu bytes of shared memory: %s", wide, cudaGetErrorString(err));
+        return -2;
+      }
+      configured[which] = wide;
+    }
+    dim3 wide_grid((vdim + WIDE - 1) / WIDE, heads, num_seqs);
+    decay_prepare_kernel<T><<<dim3(tokens, heads), 128, 0, stream>>>((const T*)rows, ld, q_off, k_off, heads, dim, activation,
+                                                                     cos_table, sin_table, table_positions, rotary, k_scale,
+                                                                     positions, prepared, status);
+    decay_scan_wide_kernel<T><<<wide_grid, 256, wide, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim,
+                                                                activation, decay, state, slots, q_start, out);
+    return tge_launched("decay_scan_wide", 2);
+  }
+  if (chunks_ok && prepared != nullptr && max_q_len >= CHUNK / 2 && dim <= 256 && chunked <= 200 * 1024) {
     static size_t configured[2] = {0, 0};
     const int which = sizeof(T) == 2 ? 1 : 0;
     if (chunked > 48 * 1024 && chunked > configured[which]) {
@@ -551,21 +838,31 @@ int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int 
       }
       configured[which] = chunked;
     }
-    decay_scan_chunked_kernel<T><<<grid, CHUNK_THREADS, chunked, stream>>>(
-        (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table, table_positions, rotary,
-        k_scale, decay, state, slots, q_start, positions, out, status);
-    return tge_launched("decay_scan_chunked", 1);
+    decay_prepare_kernel<T><<<dim3(tokens, heads), 128, 0, stream>>>((const T*)rows, ld, q_off, k_off, heads, dim, activation,
+                                                                     cos_table, sin_table, table_positions, rotary, k_scale,
+                                                                     positions, prepared, status);
+    decay_scan_chunked_kernel<T><<<grid, CHUNK_THREADS, chunked, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim,
+                                                                          activation, decay, state, slots, q_start, out);
+    return tge_launched("decay_scan_chunked", 2);
   }
-  const size_t smem = (size_t)(2 * SCAN_TOKENS * dim + SCAN_WARPS * SCAN_TOKENS * 32) * sizeof(float);
   const int per_warp = (dim + SCAN_WARPS - 1) / SCAN_WARPS;
-#define TGE_SCAN(ROWS)                                                                                            \
-  decay_scan_kernel<T, ROWS><<<grid, SCAN_WARPS * 32, smem, stream>>>(                                            \
-      (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table, table_positions, \
-      rotary, k_scale, decay, state, slots, q_start, positions, out, status)
-  if (per_warp <= 8) TGE_SCAN(8);
-  else if (per_warp <= 16) TGE_SCAN(16);
-  else if (per_warp <= 32) TGE_SCAN(32);
-  else TGE_SCAN(64);
+#define TGE_SCAN(ROWS, TOKENS)                                                                                    \
+  decay_scan_kernel<T, ROWS, TOKENS>                                                                              \
+      <<<grid, SCAN_WARPS * 32, (size_t)(2 * TOKENS * dim + SCAN_WARPS * TOKENS * 32) * sizeof(float), stream>>>( \
+          (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,            \
+          table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, status)
+#define TGE_SCAN_ROWS(TOKENS)                  \
+  do {                                         \
+    if (per_warp <= 8) TGE_SCAN(8, TOKENS);    \
+    else if (per_warp <= 16) TGE_SCAN(16, TOKENS); \
+    else if (per_warp <= 32) TGE_SCAN(32, TOKENS); \
+    else TGE_SCAN(64, TOKENS);                 \
+  } while (0)
+  // a step of single tokens walks one token per request: the kernel without the eight-token round needs far
+  // fewer registers, so more blocks share an SM while they wait for their state
+  if (max_q_len <= 1) TGE_SCAN_ROWS(1);
+  else TGE_SCAN_ROWS(SCAN_TOKENS);
+#undef TGE_SCAN_ROWS
 #undef TGE_SCAN
   return tge_launched("decay_scan", 1);
 }
@@ -586,6 +883,19 @@ TGE_API int tge_scale_add_norm(float* x, const float* y, long long ldy, const fl
   TGE_REQUIRE(rows >= 0 && hidden > 0 && ldy >= hidden, "scale_add_norm: bad shape (%d rows of %d)", rows, hidden);
   TGE_REQUIRE(eps > 0.0f, "scale_add_norm: eps must be positive");
   if (rows == 0) return 0;
+  const bool aligned = hidden % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) &&
+                       ((uintptr_t)weight % 16 == 0) && ((uintptr_t)copy % 8 == 0);
+  if (aligned && hidden <= 16 * 1024) {
+    int threads = ((hidden / 4 + 3) / 4 + 31) / 32 * 32;
+    threads = threads < 32 ? 32 : threads;
+    if (copy != nullptr && copy_is_bf16)
+      tge_launch(scale_add_norm_vec_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, y, ldy, weight,
+                 (__nv_bfloat16*)copy, hidden, alpha, eps);
+    else
+      tge_launch(scale_add_norm_vec_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, y, ldy, weight, (float*)copy,
+                 hidden, alpha, eps);
+    return tge_launched("scale_add_norm", 1);
+  }
   if (copy != nullptr && copy_is_bf16)
     scale_add_norm_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(x, y, ldy, weight, (__nv_bfloat16*)copy, hidden, alpha, eps);
   else
@@ -597,7 +907,7 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
                            int dim, int vdim, int activation, const float* cos_table, const float* sin_table,
                            int table_positions, int rotary, float k_scale, const float* decay, float* state,
                            const int* slots, const int* q_start, const int* positions, float* out, int num_seqs,
-                           int tokens, int max_q_len, int* status, cudaStream_t stream) {
+                           int tokens, int max_q_len, float* prepared, int* status, cudaStream_t stream) {
   TGE_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && dim <= 64 * SCAN_WARPS, "decay_scan: %d heads of %d x %d (keys up to %d)",
               heads, dim, vdim, 64 * SCAN_WARPS);
   TGE_REQUIRE(rotary >= 0 && rotary % 2 == 0 && rotary <= dim, "decay_scan: %d rotated elements of %d", rotary, dim);
@@ -608,10 +918,10 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
   if (is_bf16)
     return launch_decay_scan<__nv_bfloat16>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table,
                                             sin_table, table_positions, rotary, k_scale, decay, state, slots, q_start,
-                                            positions, out, num_seqs, max_q_len, status, stream);
+                                            positions, out, num_seqs, tokens, max_q_len, prepared, status, stream);
   return launch_decay_scan<float>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,
                                   table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, num_seqs,
-                                  max_q_len, status, stream);
+                                  tokens, max_q_len, prepared, status, stream);
 }
 
 TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long long ld_gate, const float* weight, void* out,
