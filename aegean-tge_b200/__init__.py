@@ -1,5 +1,7 @@
-"""A small, whole inference engine for one B200, from token ids to next token: the Qwen2.5 dense decoder and the
-Lepizen decoder (parallel blocks, attention with sinks and normalised projections, capped logits).
+"""A small, whole inference engine for one B200, from token ids to next token: the Qwen2.5 dense decoder, the
+Lepizen decoder (parallel blocks, attention with sinks and normalised projections, capped logits) and the Mozepel
+decoder (layers that normalise after the sum, decayed linear attention with a state per request, a window attention
+with pooled blocks).
 
 Public entry points:
 
@@ -10,7 +12,7 @@ Public entry points:
 """
 from . import models as _models  # noqa: F401  (registers architectures)
 from . import parts as _parts    # noqa: F401  (registers parts)
-from .config import ConfigError, LepizenConfig, Qwen2Config
+from .config import ConfigError, LepizenConfig, MozepelConfig, Qwen2Config
 from .registry import architecture_of, register_architecture, registered_architectures
 from .sampling import SamplingParams
 from .weights import WeightError, write_random_model
@@ -26,5 +28,5 @@ def __getattr__(name):
     raise AttributeError(name)
 
 
-__all__ = ["Engine", "SamplingParams", "ConfigError", "LepizenConfig", "Qwen2Config", "WeightError", "write_random_model",
+__all__ = ["Engine", "SamplingParams", "ConfigError", "LepizenConfig", "MozepelConfig", "Qwen2Config", "WeightError", "write_random_model",
            "architecture_of", "register_architecture", "registered_architectures", "__version__"]

@@ -284,10 +284,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
   const int slot = slots[seq];
   const float c = decay[head];
   float* mine = state + (((size_t)slot * heads + head) * dim) * vdim;
-  if (tid == 0) {
-    float power = 1.0f;
-    for (int m = 0; m <= CHUNK; ++m) { pw[m] = power; power *= c; }
-  }
+  if (tid <= CHUNK) pw[tid] = (float)pow((double)c, (double)tid);      // each power rounded once
   for (int e = tid; e < dim * 32; e += CHUNK_THREADS) {
     const int i = e >> 5, col = column0 + (e & 31);
     Ss[e] = col < vdim ? mine[(size_t)i * vdim + col] : 0.0f;
@@ -461,10 +458,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
   };
   fetch_qk(first);
   fetch_v(first);
-  if (tid == 0) {
-    float power = 1.0f;
-    for (int m = 0; m <= WIDE; ++m) { pw[m] = power; power *= c; }
-  }
+  if (tid <= WIDE) pw[tid] = (float)pow((double)c, (double)tid);       // each power rounded once
   for (int e = tid; e < dim * WIDE; e += 256) {
     const int i = e >> 6, col = column0 + (e & 63);
     Ss[e] = col < vdim ? mine[(size_t)i * vdim + col] : 0.0f;
