@@ -366,7 +366,7 @@ class CacheManager:
 
     def pages_missing(self, request: Hashable, total_tokens: int, computed_tokens: Optional[int] = None) -> List[int]:
         """Per group, pages that must be allocated so the request covers ``total_tokens`` positions."""
-        out = (ctypes.c_int * 8)()
+        out = (ctypes.c_int * _rt.MAX_GROUPS)()
         handle = self._handles.get(request, 0)
         count = self._lib.tge_rt_cache_pages_missing(self._cache, handle, int(total_tokens), out)
         return list(out[:count])

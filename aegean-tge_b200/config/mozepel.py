@@ -149,8 +149,8 @@ def _window_attention(where: str, m: Dict[str, Any]) -> WindowAttention:
     if not isinstance(mask, dict):
         raise ConfigError(f"config.json: missing object {where}'mask' (with 'size')")
     conv = 0 if m.get("conv") is None else _int(where, m, "conv", minimum=0)
-    if conv > 8:
-        raise ConfigError(f"config.json: {where}'conv' has {conv} taps; at most 8")
+    if conv > 16:
+        raise ConfigError(f"config.json: {where}'conv' has {conv} taps; at most 16")
     pool = 0 if mask.get("pool") is None else _int(where + "mask.", mask, "pool", minimum=0)
     return WindowAttention(heads=heads, kv_heads=kv_heads, dim=dim, vdim=_int(where, m, "vdim"),
                            scale=_number(where, m, "scale"), conv=conv, window=_int(where + "mask.", mask, "size"),

@@ -257,7 +257,7 @@ int pack_step(TgeRtCache* cache, const std::vector<PortionView>& portions, int v
               int fixed_width, int pad_rows, bool reserve, int* out, long long capacity, TgeRtStepLayout* layout) {
   int S = (int)portions.size();
   if (S == 0) return fail(TGE_RT_VALUE_ERROR, "step: no portions");
-  if ((int)cache->groups.size() > 8) return fail(TGE_RT_VALUE_ERROR, "step: more than 8 cache groups");
+  if ((int)cache->groups.size() > TGE_RT_MAX_GROUPS) return fail(TGE_RT_VALUE_ERROR, "step: more than %d cache groups", TGE_RT_MAX_GROUPS);
   // validate before touching anything
   {
     std::unordered_set<int64_t> seen;
@@ -554,7 +554,7 @@ TgeRtCache* tge_rt_cache_create(int page_size, int max_requests) {
 void tge_rt_cache_destroy(TgeRtCache* cache) { delete cache; }
 int tge_rt_cache_add_group(TgeRtCache* cache, int window) { return tge_rt_cache_add_group_strided(cache, window, 1); }
 int tge_rt_cache_add_group_strided(TgeRtCache* cache, int window, int stride) {
-  if (cache->groups.size() >= 8) return fail(TGE_RT_VALUE_ERROR, "cache manager: at most 8 groups");
+  if (cache->groups.size() >= TGE_RT_MAX_GROUPS) return fail(TGE_RT_VALUE_ERROR, "cache manager: at most %d groups", TGE_RT_MAX_GROUPS);
   TgeRtCache::Group group;
   if (stride <= 0) return fail(TGE_RT_VALUE_ERROR, "cache manager: a group keeps one entry per %d positions", stride);
   group.window = window;

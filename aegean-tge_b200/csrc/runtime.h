@@ -75,10 +75,12 @@ int tge_rt_cache_advance(TgeRtCache* cache, const int64_t* requests, const int* 
 // Sections of the packed int32 buffer, in this order; TgeRtStepLayout gives where each begins.
 //   token_ids[T] positions[T] seq_of_token[T] q_start[S+1] start_pos[S] ctx_len[S] slots[S] logit_rows[R]
 //   then one block table [S, width_g] per group
+// Cache groups a model may have: a windowed attention with pooled blocks takes two per distinct (window, block).
+#define TGE_RT_MAX_GROUPS 32
 typedef struct TgeRtStepLayout {
   int num_tokens, num_seqs, num_rows, max_q_len, max_ctx_len, total_ints;
   int token_ids, positions, seq_of_token, q_start, start_pos, ctx_len, slots, logit_rows;
-  int table[8], width[8];
+  int table[TGE_RT_MAX_GROUPS], width[TGE_RT_MAX_GROUPS];
 } TgeRtStepLayout;
 
 // Reserves what the step needs (admits unknown requests, grows pages; all or nothing) and packs it.

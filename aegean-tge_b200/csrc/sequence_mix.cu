@@ -406,6 +406,7 @@ __global__ void __launch_bounds__(CHUNK_THREADS) decay_scan_chunked_kernel(
 // memory feeds sixteen multiply-adds.  q and k are kept transposed ([element][token]) for that.
 constexpr int WIDE = 64;                 // tokens per chunk and columns per block
 constexpr int WIDE_LD = WIDE + 4;        // row stride of the transposed tiles: 16-byte aligned
+constexpr int SEGMENT = 256;             // tokens per segment when one portion is shared out over many blocks
 
 __device__ __forceinline__ void copy16_async(float* dst_shared, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst_shared)), "l"(src));
@@ -413,11 +414,17 @@ __device__ __forceinline__ void copy16_async(float* dst_shared, const float* src
 __device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
-template <typename T>
+// MODE 0: a block walks a request's whole portion from the state in its slot and leaves the new state there.
+// One long prompt then keeps only heads x (vdim / 64) blocks busy, so such steps cut every portion into segments
+// of `segment` tokens and run three launches: MODE 1 (a block per segment: the segment's own contribution to the
+// state, from zero, into `carry[segment]`), `decay_segment_carry_kernel` (per request, in order: carry[k] <- the
+// state the segment starts from, state <- c^len state + contribution; the last one goes to the slot), MODE 2 (a
+// block per segment: the readout, from carry[segment]).  blockIdx.z counts segments over all requests of the step.
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     const T* __restrict__ rows, long long ld, const float* __restrict__ prepared, int v_off, int heads, int dim, int vdim,
     int activation, const float* __restrict__ decay, float* __restrict__ state, const int* __restrict__ slots,
-    const int* __restrict__ q_start, float* __restrict__ out) {
+    const int* __restrict__ q_start, float* __restrict__ out, float* __restrict__ carry, int num_seqs, int segment) {
   extern __shared__ __align__(16) float shared[];
   float* Qt = shared;                         // [dim][WIDE_LD]   q, element-major
   float* Kt = Qt + dim * WIDE_LD;             // [dim][WIDE_LD]   k, element-major
@@ -428,21 +435,43 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
   float* pw = Ss + dim * WIDE;                // c^0 .. c^WIDE
   float* stage = pw + WIDE + 4;               // [WIDE][2 dim]: the next chunk's q and k on their way in (dim % 4 == 0)
   const int tid = threadIdx.x;
-  const int head = blockIdx.y, seq = blockIdx.z;
+  const int head = blockIdx.y;
   const int column0 = blockIdx.x * WIDE;
-  const int first = q_start[seq], last = q_start[seq + 1];
-  if (first >= last) return;
-  const int slot = slots[seq];
+  int seq = -1, first = 0, last = 0;
+  if (MODE == 0) {
+    seq = blockIdx.z;
+    first = q_start[seq];
+    last = q_start[seq + 1];
+  } else {
+    int z = blockIdx.z;
+    for (int s = 0; s < num_seqs; ++s) {
+      const int begin = q_start[s], count = q_start[s + 1] - begin;
+      const int pieces = (count + segment - 1) / segment;
+      if (z < pieces) {
+        seq = s;
+        first = begin + z * segment;
+        last = min(first + segment, begin + count);
+        break;
+      }
+      z -= pieces;
+    }
+  }
+  if (seq < 0 || first >= last) return;
   const float c = decay[head];
-  float* mine = state + (((size_t)slot * heads + head) * dim) * vdim;
+  // where the block's state comes from and goes to
+  float* mine = MODE == 0 ? state + (((size_t)slots[seq] * heads + head) * dim) * vdim
+                          : carry + (((size_t)blockIdx.z * heads + head) * dim) * vdim;
   // A chunk's q and k (prepared rows, 2 dim floats per token and head) are copied asynchronously into `stage` while
   // the chunk before is worked on, and its values wait in registers: the products never wait for memory.
-  const int quads_per_token = dim >> 1;       // 16-byte pieces of a row of 2 dim floats
+  // 16-byte pieces of a row of 2 dim floats; the launch that only builds a segment's state needs the k half alone
+  const int quads_per_token = MODE == 1 ? dim >> 2 : dim >> 1;
+  const int quad_offset = MODE == 1 ? dim : 0;
   auto fetch_qk = [&](int from) {
     const int count = min(WIDE, last - from);
     for (int e = tid; e < count * quads_per_token; e += 256) {
       const int t = e / quads_per_token, piece = e - t * quads_per_token;
-      copy16_async(stage + (size_t)t * 2 * dim + 4 * piece, prepared + ((size_t)(from + t) * heads + head) * 2 * dim + 4 * piece);
+      copy16_async(stage + (size_t)t * 2 * dim + quad_offset + 4 * piece,
+                   prepared + ((size_t)(from + t) * heads + head) * 2 * dim + quad_offset + 4 * piece);
     }
     copies_commit();
   };
@@ -461,7 +490,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
   if (tid <= WIDE) pw[tid] = (float)pow((double)c, (double)tid);       // each power rounded once
   for (int e = tid; e < dim * WIDE; e += 256) {
     const int i = e >> 6, col = column0 + (e & 63);
-    Ss[e] = col < vdim ? mine[(size_t)i * vdim + col] : 0.0f;
+    Ss[e] = (MODE != 1 && col < vdim) ? mine[(size_t)i * vdim + col] : 0.0f;
   }
   const int ty = tid >> 4, tx = tid & 15;
   const int t0 = ty * 4, c0 = tx * 4;                    // a thread's four rows (tokens) and four columns
@@ -472,7 +501,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     for (int e = tid; e < WIDE * dim; e += 256) {
       const int t = e / dim, i = e - t * dim;
       const bool live = t < n;
-      Qt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + i] : 0.0f;
+      if (MODE != 1) Qt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + i] : 0.0f;
       Kt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + dim + i] : 0.0f;
     }
 #pragma unroll
@@ -489,7 +518,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
       fetch_v(base + WIDE);
     }
     // scores of the chunk, decayed: tokens t0 .. t0 + 3 against keys c0 .. c0 + 3, tiles at or below the diagonal
-    if (c0 <= t0) {
+    if (MODE != 1 && c0 <= t0) {
       float acc[4][4] = {};
 #pragma unroll 4
       for (int i = 0; i < dim; ++i) {
@@ -514,7 +543,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     }
     __syncthreads();
     // readout: tokens t0 .. t0 + 3, columns c0 .. c0 + 3 of the block
-    {
+    if (MODE != 1) {
       float acc[4][4] = {};
 #pragma unroll 4
       for (int i = 0; i < dim; ++i) {
@@ -555,8 +584,8 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
       }
     }
     __syncthreads();
-    // state: rows 8 ty .. 8 ty + 7, columns c0 .. c0 + 3
-    {
+    // state: rows 8 ty .. 8 ty + 7, columns c0 .. c0 + 3 (nobody reads it after a segment's last readout)
+    if (MODE != 2 || base + WIDE < last) {
       float acc[8][4] = {};
       const int i0 = ty * 8;
 #pragma unroll 2
@@ -585,10 +614,39 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     }
   }
   __syncthreads();
-  for (int e = tid; e < dim * WIDE; e += 256) {
-    const int i = e >> 6, col = column0 + (e & 63);
-    if (col < vdim) mine[(size_t)i * vdim + col] = Ss[e];
+  if (MODE != 2) {
+    for (int e = tid; e < dim * WIDE; e += 256) {
+      const int i = e >> 6, col = column0 + (e & 63);
+      if (col < vdim) mine[(size_t)i * vdim + col] = Ss[e];
+    }
   }
+}
+
+// Between the two segment launches: every request's segments in order.  carry[k] holds segment k's own contribution
+// on the way in and the state it starts from on the way out; the request's slot gets the state after its last one.
+__global__ void decay_segment_carry_kernel(float* __restrict__ carry, float* __restrict__ state, const float* __restrict__ decay,
+                                           const int* __restrict__ slots, const int* __restrict__ q_start, int heads,
+                                           int dim, int vdim, int segment) {
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int cells = dim * vdim;
+  if (e >= cells) return;
+  int before = 0;
+  for (int s = 0; s < seq; ++s) before += (q_start[s + 1] - q_start[s] + segment - 1) / segment;
+  const int count = q_start[seq + 1] - q_start[seq];
+  if (count <= 0) return;
+  const int pieces = (count + segment - 1) / segment;
+  const double c = (double)decay[head];
+  float* slot = state + ((size_t)slots[seq] * heads + head) * cells + e;
+  float running = *slot;
+  for (int k = 0; k < pieces; ++k) {
+    float* cell = carry + ((size_t)(before + k) * heads + head) * cells + e;
+    const float own = *cell;
+    *cell = running;
+    const int length = min(segment, count - k * segment);
+    running = fmaf((float)pow(c, (double)length), running, own);
+  }
+  *slot = running;
 }
 
 // out[t, g*size + e] = o[t, g*size + e] / rms_g(o[t]) * weight[g*size + e] * act(gate[t, g*size + e]); one warp per
@@ -622,7 +680,7 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict
 // inputs from before the portion come from the request's convolution state [slots, taps-1, channels] (oldest first),
 // which is zero for a request that starts.  q goes to `q_out`, k and v into their pages.
 constexpr int CNR_PER_LANE = 8;    // head sizes up to 256
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(128) conv_norm_rope_store_kernel(
@@ -795,7 +853,7 @@ template <typename T>
 int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int v_off, int heads, int dim, int vdim,
                       int activation, const float* cos_table, const float* sin_table, int table_positions, int rotary,
                       float k_scale, const float* decay, float* state, const int* slots, const int* q_start,
-                      const int* positions, float* out, int num_seqs, int tokens, int max_q_len, float* prepared, int* status,
+                      const int* positions, float* out, int num_seqs, int tokens, int max_q_len, float* prepared, float* carry, int* status,
                       cudaStream_t stream) {
   dim3 grid((vdim + 31) / 32, heads, num_seqs);
   // portions of some length go chunk by chunk; single tokens and short portions token by token
@@ -806,7 +864,11 @@ int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int 
     static size_t configured[2] = {0, 0};
     const int which = sizeof(T) == 2 ? 1 : 0;
     if (wide > configured[which]) {
-      cudaError_t err = cudaFuncSetAttribute(decay_scan_wide_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide);
+      cudaError_t err = cudaFuncSetAttribute(decay_scan_wide_kernel<T, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide);
+      if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(decay_scan_wide_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide);
+      if (err == cudaSuccess)
+        err = cudaFuncSetAttribute(decay_scan_wide_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wide);
       if (err != cudaSuccess) {
         tge_set_error("decay_scan: cannot reserve %zu bytes of shared memory: %s", wide, cudaGetErrorString(err));
         return -2;
@@ -817,8 +879,20 @@ int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int 
     decay_prepare_kernel<T><<<dim3(tokens, heads), 128, 0, stream>>>((const T*)rows, ld, q_off, k_off, heads, dim, activation,
                                                                      cos_table, sin_table, table_positions, rotary, k_scale,
                                                                      positions, prepared, status);
-    decay_scan_wide_kernel<T><<<wide_grid, 256, wide, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim,
-                                                                activation, decay, state, slots, q_start, out);
+    // few blocks and long portions: segments, so that the whole device works on one prompt
+    const long long blocks = (long long)wide_grid.x * heads * num_seqs;
+    if (carry != nullptr && max_q_len >= 2 * SEGMENT && blocks < 2LL * tge_sm_count() && tokens / SEGMENT + num_seqs <= 65535) {
+      dim3 pieces(wide_grid.x, heads, tokens / SEGMENT + num_seqs);      // an upper bound; blocks beyond the last segment leave at once
+      decay_scan_wide_kernel<T, 1><<<pieces, 256, wide, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim, activation,
+                                                                  decay, state, slots, q_start, out, carry, num_seqs, SEGMENT);
+      decay_segment_carry_kernel<<<dim3((dim * vdim + 255) / 256, heads, num_seqs), 256, 0, stream>>>(
+          carry, state, decay, slots, q_start, heads, dim, vdim, SEGMENT);
+      decay_scan_wide_kernel<T, 2><<<pieces, 256, wide, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim, activation,
+                                                                  decay, state, slots, q_start, out, carry, num_seqs, SEGMENT);
+      return tge_launched("decay_scan_segments", 4);
+    }
+    decay_scan_wide_kernel<T, 0><<<wide_grid, 256, wide, stream>>>((const T*)rows, ld, prepared, v_off, heads, dim, vdim,
+                                                                   activation, decay, state, slots, q_start, out, nullptr, num_seqs, 0);
     return tge_launched("decay_scan_wide", 2);
   }
   if (chunks_ok && prepared != nullptr && max_q_len >= CHUNK / 2 && dim <= 256 && chunked <= 200 * 1024) {
@@ -901,7 +975,7 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
                            int dim, int vdim, int activation, const float* cos_table, const float* sin_table,
                            int table_positions, int rotary, float k_scale, const float* decay, float* state,
                            const int* slots, const int* q_start, const int* positions, float* out, int num_seqs,
-                           int tokens, int max_q_len, float* prepared, int* status, cudaStream_t stream) {
+                           int tokens, int max_q_len, float* prepared, float* carry, int* status, cudaStream_t stream) {
   TGE_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && dim <= 64 * SCAN_WARPS, "decay_scan: %d heads of %d x %d (keys up to %d)",
               heads, dim, vdim, 64 * SCAN_WARPS);
   TGE_REQUIRE(rotary >= 0 && rotary % 2 == 0 && rotary <= dim, "decay_scan: %d rotated elements of %d", rotary, dim);
@@ -912,10 +986,10 @@ TGE_API int tge_decay_scan(const void* rows, int is_bf16, long long ld, int q_of
   if (is_bf16)
     return launch_decay_scan<__nv_bfloat16>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table,
                                             sin_table, table_positions, rotary, k_scale, decay, state, slots, q_start,
-                                            positions, out, num_seqs, tokens, max_q_len, prepared, status, stream);
+                                            positions, out, num_seqs, tokens, max_q_len, prepared, carry, status, stream);
   return launch_decay_scan<float>(rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,
                                   table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, num_seqs,
-                                  tokens, max_q_len, prepared, status, stream);
+                                  tokens, max_q_len, prepared, carry, status, stream);
 }
 
 TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long long ld_gate, const float* weight, void* out,

@@ -102,7 +102,7 @@ def core() -> ctypes.CDLL:
                                              _c_float, _c_ptr])
         _declare(lib, "tge_decay_scan", [_c_ptr, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                          _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
-                                         _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr])
+                                         _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr])
         _declare(lib, "tge_gated_norm", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr, _c_ptr, _c_ll, _c_int, _c_int, _c_int,
                                          _c_float, _c_int, _c_ptr])
         _declare(lib, "tge_conv_norm_rope_store", [_c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
@@ -887,12 +887,15 @@ def decay_scan(rows: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: in
     # the chunked kernels read q and k as the recurrence takes them from a buffer that one kernel fills per step
     prepared = (torch.empty((tokens, heads, 2, dim), dtype=torch.float32, device=rows.device)
                 if longest >= 16 and dim <= 256 else None)
+    # one long portion is shared out over many blocks in segments of 256 tokens: a state per segment in between
+    carry = (torch.empty((tokens // 256 + num_seqs, heads, dim, vdim), dtype=torch.float32, device=rows.device)
+             if prepared is not None and longest >= 512 and dim <= 128 and dim % 4 == 0 else None)
     lib = core()
     _check(lib.tge_decay_scan(rows.data_ptr(), int(rows.dtype == torch.bfloat16), ld, q_off, k_off, v_off, heads, dim,
                               vdim, int(activation), _ptr(cos) if rotary else None, _ptr(sin) if rotary else None,
                               table_positions, rotary, float(k_scale), decay.data_ptr(), state.data_ptr(),
                               slots.data_ptr(), q_start.data_ptr(), positions.data_ptr(), out.data_ptr(), num_seqs, tokens,
-                              longest, _ptr(prepared), status_word().data_ptr(), _stream()), lib)
+                              longest, _ptr(prepared), _ptr(carry), status_word().data_ptr(), _stream()), lib)
     return out
 
 

@@ -87,8 +87,8 @@ class GQAttention(Mixer):
             raise ValueError("attention: value_dim must be positive")
         self.taps = int(p.get("short_conv") or 0)
         self.pool = int(p.get("pool") or 0)
-        if self.taps < 0 or self.taps > 8:
-            raise ValueError(f"attention: a short convolution has 1 to 8 taps, not {self.taps}")
+        if self.taps < 0 or self.taps > 16:
+            raise ValueError(f"attention: a short convolution has 1 to 16 taps, not {self.taps}")
         if self.pool < 0 or (self.pool and self.window is None):
             raise ValueError("attention: pooled blocks need a positive size and a window")
         position: PartSpec = p.get("position", PartSpec("none"))

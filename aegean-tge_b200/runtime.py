@@ -9,6 +9,7 @@ from ctypes import POINTER, c_char_p, c_int, c_int64, c_longlong, c_void_p
 from typing import Optional
 
 OK, EXHAUSTED, PAGE_ERROR, VALUE_ERROR, STUCK = 0, -1, -2, -3, -4
+MAX_GROUPS = 32          # TGE_RT_MAX_GROUPS of csrc/runtime.h: cache groups a model may have
 
 
 class PoolExhausted(RuntimeError):
@@ -23,7 +24,7 @@ class StepLayout(ctypes.Structure):
     _fields_ = [(name, c_int) for name in
                 ("num_tokens", "num_seqs", "num_rows", "max_q_len", "max_ctx_len", "total_ints",
                  "token_ids", "positions", "seq_of_token", "q_start", "start_pos", "ctx_len", "slots", "logit_rows")]
-    _fields_ += [("table", c_int * 8), ("width", c_int * 8)]
+    _fields_ += [("table", c_int * MAX_GROUPS), ("width", c_int * MAX_GROUPS)]
 
 
 _lib: Optional[ctypes.CDLL] = None

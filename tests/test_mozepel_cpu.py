@@ -45,7 +45,7 @@ def test_config_round_trip_and_description():
 @pytest.mark.parametrize("path,value", [
     (("layers", 0, "type"), "attention"), (("layers", 0, "mixer", "decay"), [0.9]), (("layers", 0, "mixer", "decay"), [0.9, 1.5]),
     (("layers", 0, "mixer", "rot", "dims"), 5), (("layers", 0, "mixer", "rot", "dims"), 10), (("layers", 1, "mixer", "left", "kv_heads"), 3),
-    (("layers", 1, "mixer", "left", "mask"), None), (("layers", 1, "mixer", "left", "conv"), 9), (("layers", 2, "weights_of"), 2),
+    (("layers", 1, "mixer", "left", "mask"), None), (("layers", 1, "mixer", "left", "conv"), 17), (("layers", 2, "weights_of"), 2),
     (("layers", 3, "weights_of"), 2), (("layers", 2, "mlp"), None), (("layers", 1, "mlp"), {"kind": "routed", "ff": 8}),
     (("postln_alpha",), None), (("norm",), {}), (("layers", 1, "mixer", "left", "rot", "scaling", "high"), 0.5)])
 def test_config_errors_name_the_key(path, value):

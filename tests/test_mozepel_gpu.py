@@ -211,11 +211,13 @@ def test_frequencies_rescaled_by_wavelength():
 @pytest.mark.parametrize("heads,dim,vdim,rotary,activation,k_scale", [
     (3, 16, 48, 8, False, 0.25), (2, 32, 32, 32, False, 32 ** -0.5), (5, 12, 20, 0, True, 1.0), (2, 128, 64, 0, True, 1.0),
     (2, 64, 128, 64, False, 0.125), (1, 200, 70, 100, True, 0.5)])
-@pytest.mark.parametrize("cuts", [[[77]], [[40], [1], [1], [2], [33]], [[9, 1, 30], [8, 1, 30], [1, 1, 1]], [[100, 3], [31, 64], [33, 17]]])
+@pytest.mark.parametrize("cuts", [[[77]], [[40], [1], [1], [2], [33]], [[9, 1, 30], [8, 1, 30], [1, 1, 1]], [[100, 3], [31, 64], [33, 17]],
+                                  [[600, 40], [3, 700]], [[1025], [256], [513]]])
 @pytest.mark.parametrize("route", ["chunks", "tokens"])
 def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rotary, activation, k_scale, cuts, route):
     """Requests cut into portions, each step a batch; the state lives in slots that are not in order.  Steps with a
-    portion of some length go chunk by chunk (``route`` "chunks"), or every step token by token."""
+    portion of some length go chunk by chunk (``route`` "chunks"; portions of 512 tokens and more in segments that
+    blocks of their own work on), or every step token by token."""
     from aegean_tge_b200.parts.rope import rotary_tables
     gen = torch.Generator().manual_seed(heads * 1000 + dim)
     count = len(cuts[0])
@@ -224,7 +226,7 @@ def test_decayed_state_in_portions_and_batches(ops, dtype, heads, dim, vdim, rot
     decay[0] = 1.0 if heads > 1 else 0.9
     width = 2 * heads * dim + heads * vdim + 5
     data = [(torch.randn(n, width, generator=gen) * 0.7).to(dtype) for n in lengths]
-    cos, sin = rotary_tables(300.0, max(rotary, 2), 512, None, precise=True)
+    cos, sin = rotary_tables(300.0, max(rotary, 2), 2048, None, precise=True)
     cos, sin = cos.to(DEV), sin.to(DEV)
     slots = [5, 0, 3][:count]
     state = torch.randn(7, heads, dim, vdim, device=DEV)          # stale junk in every slot
