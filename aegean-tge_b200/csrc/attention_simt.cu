@@ -142,6 +142,8 @@ __global__ void __launch_bounds__(128) attention_pooled_state_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, float* __restrict__ state_o,
     float* __restrict__ state_ml, int heads, int kv_heads, int head_dim, int value_dim, float scale_log2, int window,
     int pool, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y * 4 + warp;
@@ -216,12 +218,12 @@ TGE_API int tge_attention_pooled_state(const void* q, int q_stride, const void* 
   dim3 grid(tokens, (heads + 3) / 4);
   const float scale_log2 = scale * 1.4426950408889634f;
   if (is_bf16)
-    attention_pooled_state_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    tge_launch(attention_pooled_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages, pool_table,
         pool_max_pages, pool_num_pages, page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim,
         value_dim, scale_log2, window, pool, status);
   else
-    attention_pooled_state_kernel<float><<<grid, 128, 0, stream>>>(
+    tge_launch(attention_pooled_state_kernel<float>, grid, dim3(128), 0, stream,
         (const float*)q, q_stride, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages,
         page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim, value_dim, scale_log2, window, pool,
         status);

@@ -120,6 +120,8 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32) decay_scan_kernel(
     int rotary, float k_scale, const float* __restrict__ decay, float* __restrict__ state,
     const int* __restrict__ slots, const int* __restrict__ q_start, const int* __restrict__ positions,
     float* __restrict__ out, int* status) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) float shared[];
   float* qs = shared;                                   // [TOKENS][dim]
   float* ks = qs + TOKENS * dim;                   // [TOKENS][dim]
@@ -656,6 +658,8 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const float* __restrict
                                                          long long ld_gate, const float* __restrict__ weight,
                                                          T* __restrict__ out, long long ld_out, int tokens, int groups,
                                                          int size, float eps, int act) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long unit = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (unit >= (long long)tokens * groups) return;
@@ -691,6 +695,8 @@ __global__ void __launch_bounds__(128) conv_norm_rope_store_kernel(
     const int* __restrict__ positions, const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
     int max_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int page_size,
     T* __restrict__ q_out, long long ld_q, int heads, int kv_heads, int dim, int vdim, int store, int* status) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float staged[4][32 * CNR_PER_LANE];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -789,6 +795,8 @@ template <typename T>
 __global__ void conv_state_update_kernel(const T* __restrict__ raw, long long ld, float* __restrict__ conv_state,
                                          const int* __restrict__ slots, const int* __restrict__ q_start, int taps,
                                          int channels) {
+  pdl_trigger();
+  pdl_wait();
   const int seq = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
@@ -817,6 +825,8 @@ __global__ void __launch_bounds__(128) pool_kv_kernel(
     int num_pages, T* __restrict__ kp_pages, T* __restrict__ vp_pages, const int* __restrict__ pool_table,
     int pool_max_pages, int pool_num_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ seq_of_token, int kv_heads, int dim, int vdim, int pool, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
   const int position = positions[t];
   if (position < 0 || (position + 1) % pool != 0) return;
@@ -915,10 +925,10 @@ int launch_decay_scan(const void* rows, long long ld, int q_off, int k_off, int 
   }
   const int per_warp = (dim + SCAN_WARPS - 1) / SCAN_WARPS;
 #define TGE_SCAN(ROWS, TOKENS)                                                                                    \
-  decay_scan_kernel<T, ROWS, TOKENS>                                                                              \
-      <<<grid, SCAN_WARPS * 32, (size_t)(2 * TOKENS * dim + SCAN_WARPS * TOKENS * 32) * sizeof(float), stream>>>( \
-          (const T*)rows, ld, q_off, k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table,            \
-          table_positions, rotary, k_scale, decay, state, slots, q_start, positions, out, status)
+  tge_launch(decay_scan_kernel<T, ROWS, TOKENS>, grid, dim3(SCAN_WARPS * 32),                                     \
+             (size_t)(2 * TOKENS * dim + SCAN_WARPS * TOKENS * 32) * sizeof(float), stream, (const T*)rows, ld, q_off, \
+             k_off, v_off, heads, dim, vdim, activation, cos_table, sin_table, table_positions, rotary, k_scale, decay, \
+             state, slots, q_start, positions, out, status)
 #define TGE_SCAN_ROWS(TOKENS)                  \
   do {                                         \
     if (per_warp <= 8) TGE_SCAN(8, TOKENS);    \
@@ -1000,11 +1010,11 @@ TGE_API int tge_gated_norm(const float* o, const void* gate, int is_bf16, long l
   const long long units = (long long)tokens * groups;
   const unsigned blocks = (unsigned)((units + 3) / 4);
   if (is_bf16)
-    gated_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, ld_gate, weight,
-                                                                  (__nv_bfloat16*)out, ld_out, tokens, groups, size, eps, act);
+    tge_launch(gated_norm_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, o, (const __nv_bfloat16*)gate, ld_gate,
+               weight, (__nv_bfloat16*)out, ld_out, tokens, groups, size, eps, act);
   else
-    gated_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, ld_gate, weight, (float*)out, ld_out,
-                                                          tokens, groups, size, eps, act);
+    tge_launch(gated_norm_kernel<float>, dim3(blocks), dim3(128), 0, stream, o, (const float*)gate, ld_gate, weight,
+               (float*)out, ld_out, tokens, groups, size, eps, act);
   return tge_launched("gated_norm", 1);
 }
 
@@ -1030,12 +1040,12 @@ TGE_API int tge_conv_norm_rope_store(const void* raw, int is_bf16, long long ld,
   dim3 grid(tokens, (units + 3) / 4);
   int launched = 1;
   if (is_bf16) {
-    conv_norm_rope_store_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    tge_launch(conv_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
         (const __nv_bfloat16*)raw, ld, conv_w, taps, conv_state, slots, q_start, q_norm, k_norm, eps, cos_table, sin_table,
         table_positions, rotary, positions, seq_of_token, block_table, max_pages, (__nv_bfloat16*)k_pages,
         (__nv_bfloat16*)v_pages, num_pages, page_size, (__nv_bfloat16*)q_out, ld_q, heads, kv_heads, dim, vdim, store, status);
   } else {
-    conv_norm_rope_store_kernel<float><<<grid, 128, 0, stream>>>(
+    tge_launch(conv_norm_rope_store_kernel<float>, grid, dim3(128), 0, stream,
         (const float*)raw, ld, conv_w, taps, conv_state, slots, q_start, q_norm, k_norm, eps, cos_table, sin_table,
         table_positions, rotary, positions, seq_of_token, block_table, max_pages, (float*)k_pages, (float*)v_pages,
         num_pages, page_size, (float*)q_out, ld_q, heads, kv_heads, dim, vdim, store, status);
@@ -1045,11 +1055,11 @@ TGE_API int tge_conv_norm_rope_store(const void* raw, int is_bf16, long long ld,
     // in stream order behind the kernel that read the old state
     dim3 update((channels + 127) / 128, num_seqs);
     if (is_bf16)
-      conv_state_update_kernel<__nv_bfloat16><<<update, 128, 0, stream>>>((const __nv_bfloat16*)raw, ld, conv_state, slots,
-                                                                          q_start, taps, channels);
+      tge_launch(conv_state_update_kernel<__nv_bfloat16>, update, dim3(128), 0, stream, (const __nv_bfloat16*)raw, ld,
+                 conv_state, slots, q_start, taps, channels);
     else
-      conv_state_update_kernel<float><<<update, 128, 0, stream>>>((const float*)raw, ld, conv_state, slots, q_start, taps,
-                                                                  channels);
+      tge_launch(conv_state_update_kernel<float>, update, dim3(128), 0, stream, (const float*)raw, ld, conv_state, slots,
+                 q_start, taps, channels);
     ++launched;
   }
   return tge_launched("conv_state_update", launched);
@@ -1063,12 +1073,12 @@ TGE_API int tge_pool_kv(const void* k_pages, const void* v_pages, int is_bf16, c
   if (tokens == 0) return 0;
   dim3 grid(tokens, kv_heads);
   if (is_bf16)
-    pool_kv_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    tge_launch(pool_kv_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, max_pages, num_pages,
         (__nv_bfloat16*)kp_pages, (__nv_bfloat16*)vp_pages, pool_table, pool_max_pages, pool_num_pages, page_size, positions,
         seq_of_token, kv_heads, dim, vdim, pool, status);
   else
-    pool_kv_kernel<float><<<grid, 128, 0, stream>>>((const float*)k_pages, (const float*)v_pages, block_table, max_pages,
+    tge_launch(pool_kv_kernel<float>, grid, dim3(128), 0, stream, (const float*)k_pages, (const float*)v_pages, block_table, max_pages,
                                                      num_pages, (float*)kp_pages, (float*)vp_pages, pool_table,
                                                      pool_max_pages, pool_num_pages, page_size, positions, seq_of_token,
                                                      kv_heads, dim, vdim, pool, status);
