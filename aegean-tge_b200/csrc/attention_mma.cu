@@ -58,10 +58,7 @@ struct AttnParams {
   float* partial_o;
   float* partial_ml;
   int* status;
-  // one more split state per (token, head), computed elsewhere (pooled blocks), that joins the merge of the splits:
-  // [tokens, heads, DV] unnormalised sums and [tokens, heads, 2] (maximum in base-2 units, denominator); may be null
-  const float* extra_o;
-  const float* extra_ml;
+  int leave_states;          // the key runs' states stay unmerged in the scratch memory: the caller merges them
   int q_stride, out_stride;
   int max_pages, num_pages, page_size, page_shift;
   int num_seqs, total_tokens;
@@ -1197,8 +1194,7 @@ template <int HELD>                                                  // splits w
 __global__ void attention_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                        const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                                        int out_stride, int total_tokens, int heads, int window, int split_tokens,
-                                       int num_splits, int first_token, const float* __restrict__ sink,
-                                       const float* __restrict__ extra_o, const float* __restrict__ extra_ml) {
+                                       int num_splits, int first_token, const float* __restrict__ sink) {
   pdl_trigger();
   const int t = blockIdx.x + first_token, h = blockIdx.y;
   const int pos = positions[t];                                     // given to the step: not the previous kernel's work
@@ -1206,8 +1202,6 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
   pdl_wait();
   const size_t stride = (size_t)total_tokens * heads;               // slots per split
   const size_t slot0 = (size_t)t * heads + h;
-  // the state that came from elsewhere is one more split, last in the order; without keys it is (-inf, 0)
-  const float2 extra = extra_ml != nullptr ? *reinterpret_cast<const float2*>(extra_ml + slot0 * 2) : make_float2(-INFINITY, 0.0f);
   if (num_splits <= HELD) {
     // Every load is asked for before the first result is needed, the row's position among them: one round
     // trip instead of four.  Splits without a key visible to the row are read too (the scratch holds all
@@ -1230,7 +1224,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
         ml[i] = live ? ml[i] : make_float2(-INFINITY, 0.0f);
         o[i] = live ? o[i] : 0.0f;
       }
-      float m = extra.x;
+      float m = -INFINITY;
 #pragma unroll
       for (int i = 0; i < HELD; ++i) m = fmaxf(m, ml[i].x);
       const float m_use = m == -INFINITY ? 0.0f : m;
@@ -1241,11 +1235,6 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
         l += scale * ml[i].y;
         acc += scale * o[i];
       }
-      if (extra_o != nullptr) {
-        const float scale = exp2f(extra.x - m_use);
-        l += scale * extra.y;
-        acc += scale * extra_o[slot0 * DV + d];
-      }
       if (sink != nullptr) l += exp2f(sink_log2 - m_use);
       out[(size_t)t * out_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * (l > 0.0f ? 1.0f / l : 0.0f));
     }
@@ -1254,7 +1243,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
   const int first_key = window > 0 ? max(pos - window + 1, 0) : 0;
   const int s_lo = first_key / split_tokens;
   const int s_hi = min(pos / split_tokens, num_splits - 1);
-  float m = extra.x;
+  float m = -INFINITY;
   for (int s = s_lo; s <= s_hi; ++s) m = fmaxf(m, partial_ml[((size_t)s * stride + slot0) * 2]);
   const float m_use = m == -INFINITY ? 0.0f : m;
   float l = 0.0f;
@@ -1262,8 +1251,6 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
     const size_t slot = (size_t)s * stride + slot0;
     l += exp2f(partial_ml[slot * 2] - m_use) * partial_ml[slot * 2 + 1];
   }
-  const float extra_scale = exp2f(extra.x - m_use);
-  if (extra_o != nullptr) l += extra_scale * extra.y;
   if (sink != nullptr) l += exp2f(sink_log2 - m_use);
   const float inv = l > 0.0f ? 1.0f / l : 0.0f;
   for (int d = threadIdx.x; d < DV; d += blockDim.x) {
@@ -1272,7 +1259,6 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
       const size_t slot = (size_t)s * stride + slot0;
       acc += exp2f(partial_ml[slot * 2] - m_use) * partial_o[slot * DV + d];
     }
-    if (extra_o != nullptr) acc += extra_scale * extra_o[slot0 * DV + d];
     out[(size_t)t * out_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -1281,14 +1267,14 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial_o, cons
 // instance, and beyond that the kernel walks the splits in a loop.
 void launch_merge(dim3 grid, cudaStream_t stream, const float* partial_o, const float* partial_ml, const int* positions,
                   __nv_bfloat16* out, int out_stride, int total_tokens, int heads, int window, int split_tokens,
-                  int num_splits, int first_token, const float* sink, const float* extra_o, const float* extra_ml) {
+                  int num_splits, int first_token, const float* sink) {
   const int threads = DV >= 128 ? 128 : (DV >= 64 ? 64 : 32);
   if (num_splits <= 16)
     tge_launch(attention_merge_kernel<16>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
-               total_tokens, heads, window, split_tokens, num_splits, first_token, sink, extra_o, extra_ml);
+               total_tokens, heads, window, split_tokens, num_splits, first_token, sink);
   else
     tge_launch(attention_merge_kernel<48>, grid, threads, 0, stream, partial_o, partial_ml, positions, out, out_stride,
-               total_tokens, heads, window, split_tokens, num_splits, first_token, sink, extra_o, extra_ml);
+               total_tokens, heads, window, split_tokens, num_splits, first_token, sink);
 }
 
 template <int NWARPS>
@@ -1329,8 +1315,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int first_token, const float* sink, const float* extra_o, const float* extra_ml,
-                              cudaStream_t stream) {
+                              int first_token, const float* sink, int leave_states, cudaStream_t stream) {
   TGE_REQUIRE(tokens >= 0 && num_seqs >= 0, "attention_mma: negative sizes");
   TGE_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention_mma: heads %d must be a positive multiple of kv heads %d", heads, kv_heads);
@@ -1347,7 +1332,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.q = (const __nv_bfloat16*)q; p.k_pages = (const __nv_bfloat16*)k_pages; p.v_pages = (const __nv_bfloat16*)v_pages;
   p.block_table = block_table; p.q_start = q_start; p.start_pos = start_pos;
   p.out = (__nv_bfloat16*)out; p.status = status; p.sink = sink;
-  p.extra_o = extra_o; p.extra_ml = extra_ml;
+  p.leave_states = leave_states;
   p.q_stride = q_stride; p.out_stride = out_stride;
   p.max_pages = max_pages; p.num_pages = num_pages; p.page_size = page_size;
   p.page_shift = 0;
@@ -1363,8 +1348,7 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   p.split_tokens = split_tokens > 0 ? split_tokens : max_ctx_len;
   p.num_splits = num_splits;
   TGE_REQUIRE(num_splits == 1 || scratch != nullptr, "attention_mma: %d splits need scratch memory", num_splits);
-  TGE_REQUIRE((extra_o == nullptr) == (extra_ml == nullptr) && (extra_o == nullptr || num_splits > 1),
-              "attention_mma: a state from elsewhere joins the merge of at least two splits (both of its arrays given)");
+  TGE_REQUIRE(!leave_states || num_splits > 1, "attention_mma: states are left unmerged only when the keys are cut");
   p.partial_o = scratch;
   p.partial_ml = scratch ? scratch + (size_t)num_splits * tokens * heads * DV : nullptr;
 
@@ -1404,9 +1388,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     else tge_launch(attention_decode_tma_kernel<1>, grid, DEC_TMA_THREADS, smem, stream, *map_k, *map_v, p);
     int rc = tge_check_launch("attention_decode_tma");
     if (rc != 0) return rc;
-    if (num_splits > 1) {
+    if (num_splits > 1 && !p.leave_states) {
       dim3 mgrid(tokens - first_token, heads);
-      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1431,9 +1415,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
     tge_launch(attention_decode_kernel, grid, DEC_WARPS * 32, smem, stream, p);
     int rc = tge_check_launch("attention_decode");
     if (rc != 0) return rc;
-    if (num_splits > 1) {
+    if (num_splits > 1 && !p.leave_states) {
       dim3 mgrid(tokens - first_token, heads);
-      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+      launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
       return tge_launched("attention_merge", 2);
     }
     return 1;
@@ -1467,9 +1451,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
         tge_launch(tc2::attention_prefill_tc2_kernel, grid2, tc2::THREADS, smem2, stream, *map_k, *map_v, p);
         int rc2 = tge_check_launch("attention_prefill_tc2");
         if (rc2 != 0) return rc2;
-        if (num_splits > 1) {
+        if (num_splits > 1 && !p.leave_states) {
           dim3 mgrid(tokens - first_token, heads);
-          launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+          launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
           return tge_launched("attention_merge", 2);
         }
         return 1;
@@ -1489,9 +1473,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       tge_launch(tc::attention_prefill_tc_kernel, grid, tc::THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tc");
       if (rc != 0) return rc;
-      if (num_splits > 1) {
+      if (num_splits > 1 && !p.leave_states) {
         dim3 mgrid(tokens - first_token, heads);
-        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1512,9 +1496,9 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
       tge_launch(attention_prefill_tma_kernel, grid, PRE_THREADS, smem, stream, *map_k, *map_v, p);
       int rc = tge_check_launch("attention_prefill_tma");
       if (rc != 0) return rc;
-      if (num_splits > 1) {
+      if (num_splits > 1 && !p.leave_states) {
         dim3 mgrid(tokens - first_token, heads);
-        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+        launch_merge(mgrid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
         return tge_launched("attention_merge", 2);
       }
       return 1;
@@ -1532,14 +1516,17 @@ static int attention_dispatch(const void* q, int q_stride, const void* k_pages, 
   else if (nwarps == 2) rc = launch<2>(p, tiles, stream);
   else rc = launch<4>(p, tiles, stream);
   if (rc != 0) return rc;
-  if (num_splits > 1) {
+  if (num_splits > 1 && !p.leave_states) {
     dim3 grid(tokens - first_token, heads);
-    launch_merge(grid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink, p.extra_o, p.extra_ml);
+    launch_merge(grid, stream, p.partial_o, p.partial_ml, positions, p.out, out_stride, tokens, heads, window, p.split_tokens, num_splits, first_token, p.sink);
     return tge_launched("attention_merge", 2);
   }
   return 1;
 }
 
+// `leave_states`: the keys are cut into at least two runs and the runs' unnormalised states (sums, maxima in base-2
+// units, denominators) stay in the scratch memory unmerged, [runs, tokens, heads, DV] and then [runs, tokens, heads, 2]:
+// the caller has more to merge into the softmax (pooled blocks) and writes the output itself.
 // `decode_prefix`: the caller knows that the first so many sequences of a step that also holds longer portions
 // bring one token each (0: unknown or none).  They then go to the split-key decode kernel, which reads each
 // sequence's keys once for all query heads of a kv head, instead of filling one 128-row query tile of the
@@ -1550,8 +1537,8 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
                               const int* q_start, const int* start_pos, const int* positions, int num_seqs,
                               int tokens, int max_q_len, int max_ctx_len, void* out, int out_stride, int heads,
                               int kv_heads, float scale, int window, int split_tokens, float* scratch, int* status,
-                              int decode_prefix, int prefix_split_tokens, const float* sink, const float* extra_o,
-                              const float* extra_ml, cudaStream_t stream) {
+                              int decode_prefix, int prefix_split_tokens, const float* sink, int leave_states,
+                              cudaStream_t stream) {
   TGE_REQUIRE(decode_prefix >= 0 && decode_prefix <= num_seqs, "attention_mma: %d leading single tokens of %d sequences",
               decode_prefix, num_seqs);
   TGE_REQUIRE(prefix_split_tokens >= 0 && prefix_split_tokens % BKV == 0,
@@ -1559,14 +1546,14 @@ TGE_API int tge_attention_mma(const void* q, int q_stride, const void* k_pages, 
   if (decode_prefix == 0 || max_q_len <= 1 || decode_prefix == num_seqs || kv_heads <= 0 || heads / kv_heads > 16)
     return attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start, start_pos,
                               positions, num_seqs, tokens, max_q_len, max_ctx_len, out, out_stride, heads, kv_heads, scale,
-                              window, split_tokens, scratch, status, 0, sink, extra_o, extra_ml, stream);
+                              window, split_tokens, scratch, status, 0, sink, leave_states, stream);
   const int first = attention_dispatch(q, q_stride, k_pages, v_pages, block_table, max_pages, num_pages, page_size, q_start,
                                        start_pos, positions, decode_prefix, decode_prefix, 1, max_ctx_len, out, out_stride,
-                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, extra_o, extra_ml, stream);
+                                       heads, kv_heads, scale, window, prefix_split_tokens, scratch, status, 0, sink, leave_states, stream);
   if (first < 0) return first;
   const int rest = attention_dispatch(q, q_stride, k_pages, v_pages, block_table + (size_t)decode_prefix * max_pages, max_pages,
                                       num_pages, page_size, q_start + decode_prefix, start_pos + decode_prefix, positions,
                                       num_seqs - decode_prefix, tokens, max_q_len, max_ctx_len, out, out_stride, heads,
-                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, extra_o, extra_ml, stream);
+                                      kv_heads, scale, window, split_tokens, scratch, status, decode_prefix, sink, leave_states, stream);
   return rest < 0 ? rest : first + rest;
 }

@@ -132,16 +132,19 @@ __global__ void __launch_bounds__(128) attention_simt_kernel(
   }
 }
 
-// The pooled blocks alone, as a state for the tensor-core kernels' merge of key splits: for each (token, head) the
-// unnormalised sums over the pooled entries the query sees, acc = sum_b 2^(s_b - m) v_b, with m = max_b s_b and
-// l = sum_b 2^(s_b - m), scores in base-2 units (s = q . k * scale * log2 e).  No entry seen: (m, l) = (-inf, 0).
+// For the tensor-core path: a walk over the pooled entries a query sees (scores in base-2 units, s = q . k * scale *
+// log2 e, running maximum and sum as in the kernel above), then the merge with the states that the tensor-core
+// kernels left for the window's key runs (partial_o [runs, tokens, heads, value_dim], partial_ml [runs, tokens, heads, 2]: unnormalised sums,
+// maxima in base-2 units, denominators), the runs that hold keys visible to the row in run order, and the row's
+// output.  One warp per (token, head): the pooled state never leaves its registers.
 template <typename T>
-__global__ void __launch_bounds__(128) attention_pooled_state_kernel(
+__global__ void __launch_bounds__(128) attention_pooled_merge_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ kp_pages, const T* __restrict__ vp_pages,
     const int* __restrict__ pool_table, int pool_max_pages, int pool_num_pages, int page_size,
-    const int* __restrict__ positions, const int* __restrict__ seq_of_token, float* __restrict__ state_o,
-    float* __restrict__ state_ml, int heads, int kv_heads, int head_dim, int value_dim, float scale_log2, int window,
-    int pool, int* status) {
+    const int* __restrict__ positions, const int* __restrict__ seq_of_token, const float* __restrict__ partial_o,
+    const float* __restrict__ partial_ml, int total_tokens, int num_runs, int run_tokens, T* __restrict__ out,
+    int out_stride, int heads, int kv_heads, int head_dim, int value_dim, float scale_log2, int window, int pool,
+    const float* __restrict__ sink, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -190,45 +193,33 @@ __global__ void __launch_bounds__(128) attention_pooled_state_kernel(
     }
     m = m_new;
   }
-  const size_t slot = (size_t)t * heads + h;
+  const int run_lo = first / run_tokens;
+  const int run_hi = min(pos / run_tokens, num_runs - 1);
+  for (int run = run_lo; run <= run_hi; ++run) {
+    const size_t slot = ((size_t)run * total_tokens + t) * heads + h;
+    const float2 ml = *reinterpret_cast<const float2*>(partial_ml + slot * 2);
+    if (ml.x == -INFINITY) continue;
+    const float m_new = fmaxf(m, ml.x);
+    const float mine = exp2f(m - m_new), theirs = exp2f(ml.x - m_new);
+    l = l * mine + ml.y * theirs;
+#pragma unroll
+    for (int i = 0; i < MAX_PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      if (d < value_dim) acc[i] = fmaf(partial_o[slot * value_dim + d], theirs, acc[i] * mine);
+    }
+    m = m_new;
+  }
+  if (sink != nullptr) l += exp2f(sink[h] * 1.4426950408889634f - (m == -INFINITY ? 0.0f : m));
+  const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+  T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
 #pragma unroll
   for (int i = 0; i < MAX_PER_LANE; ++i) {
     const int d = lane + 32 * i;
-    if (d < value_dim) state_o[slot * value_dim + d] = acc[i];
-  }
-  if (lane == 0) {
-    state_ml[slot * 2] = m;
-    state_ml[slot * 2 + 1] = l;
+    if (d < value_dim) orow[d] = from_float<T>(acc[i] * inv);
   }
 }
 
 }  // namespace
-
-TGE_API int tge_attention_pooled_state(const void* q, int q_stride, const void* kp_pages, const void* vp_pages,
-                                       const int* pool_table, int pool_max_pages, int pool_num_pages, int page_size,
-                                       const int* positions, const int* seq_of_token, float* state_o, float* state_ml,
-                                       int tokens, int heads, int kv_heads, int head_dim, int value_dim, float scale,
-                                       int window, int pool, int is_bf16, int* status, cudaStream_t stream) {
-  TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention: heads %d, kv heads %d", heads, kv_heads);
-  TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE && value_dim > 0 && value_dim <= 32 * MAX_PER_LANE,
-              "attention: head sizes %d and %d outside (0, %d]", head_dim, value_dim, 32 * MAX_PER_LANE);
-  TGE_REQUIRE(window > 0 && pool > 0 && page_size > 0 && pool_max_pages > 0 && pool_num_pages > 0,
-              "attention: pooled blocks need a window, their size and their pages");
-  if (tokens == 0) return 0;
-  dim3 grid(tokens, (heads + 3) / 4);
-  const float scale_log2 = scale * 1.4426950408889634f;
-  if (is_bf16)
-    tge_launch(attention_pooled_state_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
-        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages, pool_table,
-        pool_max_pages, pool_num_pages, page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim,
-        value_dim, scale_log2, window, pool, status);
-  else
-    tge_launch(attention_pooled_state_kernel<float>, grid, dim3(128), 0, stream,
-        (const float*)q, q_stride, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages,
-        page_size, positions, seq_of_token, state_o, state_ml, heads, kv_heads, head_dim, value_dim, scale_log2, window, pool,
-        status);
-  return tge_launched("attention_pooled_state", 1);
-}
 
 TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_pages, int num_pages, int page_size,
@@ -262,4 +253,34 @@ TGE_API int tge_attention_simt(const void* q, int q_stride, const void* k_pages,
         page_size, positions, seq_of_token, (float*)out, out_stride, heads, kv_heads, head_dim, value_dim, sink, scale,
         window, pool, (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, status);
   return tge_launched("attention_simt", 1);
+}
+
+TGE_API int tge_attention_pooled_merge(const void* q, int q_stride, const void* kp_pages, const void* vp_pages,
+                                       const int* pool_table, int pool_max_pages, int pool_num_pages, int page_size,
+                                       const int* positions, const int* seq_of_token, const float* partial_o,
+                                       const float* partial_ml, int num_runs, int run_tokens, void* out, int out_stride,
+                                       int tokens, int heads, int kv_heads, int head_dim, int value_dim, float scale,
+                                       int window, int pool, const float* sink, int is_bf16, int* status,
+                                       cudaStream_t stream) {
+  TGE_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "attention: heads %d, kv heads %d", heads, kv_heads);
+  TGE_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE && value_dim > 0 && value_dim <= 32 * MAX_PER_LANE,
+              "attention: head sizes %d and %d outside (0, %d]", head_dim, value_dim, 32 * MAX_PER_LANE);
+  TGE_REQUIRE(window > 0 && pool > 0 && page_size > 0 && pool_max_pages > 0 && pool_num_pages > 0,
+              "attention: pooled blocks need a window, their size and their pages");
+  TGE_REQUIRE(num_runs > 0 && run_tokens > 0 && partial_o != nullptr && partial_ml != nullptr,
+              "attention: the merge needs the key runs' states");
+  if (tokens == 0) return 0;
+  dim3 grid(tokens, (heads + 3) / 4);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (is_bf16)
+    tge_launch(attention_pooled_merge_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)q, q_stride,
+               (const __nv_bfloat16*)kp_pages, (const __nv_bfloat16*)vp_pages, pool_table, pool_max_pages, pool_num_pages,
+               page_size, positions, seq_of_token, partial_o, partial_ml, tokens, num_runs, run_tokens, (__nv_bfloat16*)out,
+               out_stride, heads, kv_heads, head_dim, value_dim, scale_log2, window, pool, sink, status);
+  else
+    tge_launch(attention_pooled_merge_kernel<float>, grid, dim3(128), 0, stream, (const float*)q, q_stride,
+               (const float*)kp_pages, (const float*)vp_pages, pool_table, pool_max_pages, pool_num_pages, page_size, positions,
+               seq_of_token, partial_o, partial_ml, tokens, num_runs, run_tokens, (float*)out, out_stride, heads, kv_heads,
+               head_dim, value_dim, scale_log2, window, pool, sink, status);
+  return tge_launched("attention_pooled_merge", 1);
 }

@@ -468,15 +468,19 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
   // 16-byte pieces of a row of 2 dim floats; the launch that only builds a segment's state needs the k half alone
   const int quads_per_token = MODE == 1 ? dim >> 2 : dim >> 1;
   const int quad_offset = MODE == 1 ? dim : 0;
-  auto fetch_qk = [&](int from) {
+  auto fetch_qk = [&](float* into, int from) {
     const int count = min(WIDE, last - from);
     for (int e = tid; e < count * quads_per_token; e += 256) {
       const int t = e / quads_per_token, piece = e - t * quads_per_token;
-      copy16_async(stage + (size_t)t * 2 * dim + quad_offset + 4 * piece,
+      copy16_async(into + (size_t)t * 2 * dim + quad_offset + 4 * piece,
                    prepared + ((size_t)(from + t) * heads + head) * 2 * dim + quad_offset + 4 * piece);
     }
     copies_commit();
   };
+  // The state-only launch reads k where the copy put it: it needs neither q nor the transposed tiles, so their room
+  // is a second staging buffer and the chunks alternate between the two.
+  float* current = stage;
+  float* other = MODE == 1 ? Qt : stage;
   float ahead[16];                            // the next chunk's values for this thread's places in Vs
   auto fetch_v = [&](int from) {
     const int count = min(WIDE, last - from);
@@ -487,7 +491,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
       ahead[k] = (t < count && col < vdim) ? to_float<T>(rows[(size_t)(from + t) * ld + v_off + head * vdim + col]) : 0.0f;
     }
   };
-  fetch_qk(first);
+  fetch_qk(current, first);
   fetch_v(first);
   if (tid <= WIDE) pw[tid] = (float)pow((double)c, (double)tid);       // each power rounded once
   for (int e = tid; e < dim * WIDE; e += 256) {
@@ -500,11 +504,13 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     const int n = min(WIDE, last - base);
     copies_wait();
     __syncthreads();                                     // the copies, the powers and the state are there; the last chunk is done with Kt, Vd
-    for (int e = tid; e < WIDE * dim; e += 256) {
-      const int t = e / dim, i = e - t * dim;
-      const bool live = t < n;
-      if (MODE != 1) Qt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + i] : 0.0f;
-      Kt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + dim + i] : 0.0f;
+    if (MODE != 1) {
+      for (int e = tid; e < WIDE * dim; e += 256) {
+        const int t = e / dim, i = e - t * dim;
+        const bool live = t < n;
+        Qt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + i] : 0.0f;
+        Kt[i * WIDE_LD + t] = live ? stage[(size_t)t * 2 * dim + dim + i] : 0.0f;
+      }
     }
 #pragma unroll
     for (int k = 0; k < 16; ++k) {
@@ -516,7 +522,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
     }
     __syncthreads();
     if (base + WIDE < last) {
-      fetch_qk(base + WIDE);
+      fetch_qk(other, base + WIDE);
       fetch_v(base + WIDE);
     }
     // scores of the chunk, decayed: tokens t0 .. t0 + 3 against keys c0 .. c0 + 3, tiles at or below the diagonal
@@ -596,7 +602,7 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           if (i0 + r < dim) {
-            const float k = Kt[(i0 + r) * WIDE_LD + j];
+            const float k = MODE == 1 ? current[(size_t)j * 2 * dim + dim + i0 + r] : Kt[(i0 + r) * WIDE_LD + j];
             acc[r][0] = fmaf(k, v4.x, acc[r][0]); acc[r][1] = fmaf(k, v4.y, acc[r][1]);
             acc[r][2] = fmaf(k, v4.z, acc[r][2]); acc[r][3] = fmaf(k, v4.w, acc[r][3]);
           }
@@ -613,6 +619,11 @@ __global__ void __launch_bounds__(256) decay_scan_wide_kernel(
           *cell = s4;
         }
       }
+    }
+    if (MODE == 1) {
+      float* swap = current;
+      current = other;
+      other = swap;
     }
   }
   __syncthreads();
@@ -641,12 +652,22 @@ __global__ void decay_segment_carry_kernel(float* __restrict__ carry, float* __r
   const double c = (double)decay[head];
   float* slot = state + ((size_t)slots[seq] * heads + head) * cells + e;
   float running = *slot;
-  for (int k = 0; k < pieces; ++k) {
-    float* cell = carry + ((size_t)(before + k) * heads + head) * cells + e;
-    const float own = *cell;
-    *cell = running;
-    const int length = min(segment, count - k * segment);
-    running = fmaf((float)pow(c, (double)length), running, own);
+  const float whole = (float)pow(c, (double)segment);                 // every segment but a request's last is whole
+  for (int k0 = 0; k0 < pieces; k0 += 16) {
+    // sixteen segments' contributions are asked for at once; the stores that follow would otherwise keep each
+    // load behind the one before
+    float own[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k)
+      own[k] = k0 + k < pieces ? carry[((size_t)(before + k0 + k) * heads + head) * cells + e] : 0.0f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (k0 + k < pieces) {
+        carry[((size_t)(before + k0 + k) * heads + head) * cells + e] = running;
+        const int length = min(segment, count - (k0 + k) * segment);
+        running = fmaf(length == segment ? whole : (float)pow(c, (double)length), running, own[k]);
+      }
+    }
   }
   *slot = running;
 }

@@ -94,9 +94,10 @@ def core() -> ctypes.CDLL:
                                              _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                                              _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
                                              _c_ptr, _c_ptr])
-        _declare(lib, "tge_attention_pooled_state", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
-                                                     _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                     _c_float, _c_int, _c_int, _c_int, _c_ptr, _c_ptr])
+        _declare(lib, "tge_attention_pooled_merge", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
+                                                     _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_int, _c_int,
+                                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
+                                                     _c_ptr])
         _declare(lib, "tge_to_run_dtype", [_c_ptr, _c_ptr, _c_int, _c_ll, _c_ptr])
         _declare(lib, "tge_scale_add_norm", [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_float,
                                              _c_float, _c_ptr])
@@ -140,7 +141,7 @@ def attention_lib(head_dim: int, value_dim: int = 0) -> ctypes.CDLL:
         _declare(lib, "tge_attention_mma", [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_ptr,
                                             _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_int,
                                             _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr,
-                                            _c_ptr, _c_ptr, _c_ptr])
+                                            _c_int, _c_ptr])
         lib.tge_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.tge_attention_mma_scratch_floats.restype = _c_ll
         if lib.tge_attention_mma_head_dim() != head_dim or lib.tge_attention_mma_value_dim() != value_dim:
@@ -770,26 +771,16 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         lib = attention_lib(head_dim, value_dim)
         prefix = decode_prefix if decode_prefix >= MIN_DECODE_PREFIX and max_q_len > 1 and not pool else 0
         prefix_split = split_tokens
-        extra_o = extra_ml = None
         if pool:
             # The window's tokens go through the tensor-core kernels with their keys cut into at least two runs, so
-            # that they leave unnormalised states; the few pooled entries a query sees become one more state, from a
-            # kernel of their own, and the merge of the runs takes it in.
-            extra_o = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=q.device)
-            extra_ml = torch.empty((tokens, heads, 2), dtype=torch.float32, device=q.device)
-            core_lib = core()
-            _check(core_lib.tge_attention_pooled_state(q.data_ptr(), q_stride, pooled_k.data_ptr(), pooled_v.data_ptr(),
-                                                       pool_table.data_ptr(), pool_width, pool_pages, page_size,
-                                                       positions.data_ptr(), seq_of_token.data_ptr(), extra_o.data_ptr(),
-                                                       extra_ml.data_ptr(), tokens, heads, kv_heads, head_dim, value_dim,
-                                                       float(scale), window, int(pool), 1, status_word().data_ptr(),
-                                                       _stream()), core_lib)
+            # that they leave unnormalised states in the scratch memory; one more kernel walks the few pooled entries
+            # a query sees, merges the runs' states into that and writes the row.
             if split_tokens == 0:
                 split_tokens = choose_attention_split(tokens, num_seqs, max_q_len, typical_ctx_len or max_ctx_len, heads,
                                                       kv_heads, bound=max_ctx_len)
             if split_tokens == 0 or split_tokens >= max_ctx_len:
                 # one run would be normalised at once: cut in two (a bound of two tiles at least; a run beyond a
-                # request's keys holds nothing and is dropped by the merge)
+                # request's keys holds nothing and is never read)
                 max_ctx_len = max(max_ctx_len, 128)
                 split_tokens = 64 * -(-max_ctx_len // 128)
         if split_tokens == 0:
@@ -808,7 +799,17 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
                                      start_pos.data_ptr(), positions.data_ptr(), num_seqs, tokens, max_q_len,
                                      max_ctx_len, out.data_ptr(), out_stride, heads, kv_heads, float(scale), window,
                                      split_tokens, _ptr(scratch), status_word().data_ptr(), prefix, prefix_split,
-                                     _ptr(sink), _ptr(extra_o), _ptr(extra_ml), _stream()), lib)
+                                     _ptr(sink), int(bool(pool)), _stream()), lib)
+        if pool:
+            core_lib = core()
+            states = scratch.data_ptr()
+            _check(core_lib.tge_attention_pooled_merge(q.data_ptr(), q_stride, pooled_k.data_ptr(), pooled_v.data_ptr(),
+                                                       pool_table.data_ptr(), pool_width, pool_pages, page_size,
+                                                       positions.data_ptr(), seq_of_token.data_ptr(), states,
+                                                       states + 4 * splits * tokens * heads * value_dim, splits, split_tokens,
+                                                       out.data_ptr(), out_stride, tokens, heads, kv_heads, head_dim,
+                                                       value_dim, float(scale), window, int(pool), _ptr(sink), 1,
+                                                       status_word().data_ptr(), _stream()), core_lib)
         return out
     lib = core()
     _check(lib.tge_attention_simt(q.data_ptr(), q_stride, k_pages.data_ptr(), v_pages.data_ptr(),
