@@ -126,6 +126,12 @@ class DecoderModel:
                     total += count * self.env.dtype.itemsize
         return total
 
+    def decode_cache_bytes(self, context: int) -> int:
+        """Bytes of cache and state a single-token step moves for one request that holds ``context`` tokens, over the
+        layers that keep their own (without windows, pooled entries or state: ``context * cache_bytes_per_token()``)."""
+        return sum(block.mixer.decode_bytes(context) for block, layer in zip(self.blocks, self.spec.layers)
+                   if layer.cache_from is None)
+
     def weight_bytes(self) -> int:
         """Bytes of all parameters on the device, a tensor that two parts share counted once."""
         total = 0

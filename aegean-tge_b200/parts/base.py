@@ -210,6 +210,30 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def decode_bytes(self, context: int) -> int:
+        """Bytes of cache and state that one single-token step moves for a request holding ``context`` tokens: the
+        entries of the positions it may read (all of them, or a window's), the whole entries among them of the caches
+        that keep one per block, and the fixed-size state read and written."""
+        def per_entry(spec) -> int:
+            total = 0
+            for _name, shape in spec.entries:
+                count = 1
+                for extent in shape:
+                    count *= int(extent)
+                total += count
+            return total
+        total = 0
+        spec = self.cache_spec()
+        if spec is not None:
+            seen = context if spec.window is None else min(context, int(spec.window))
+            total += seen * per_entry(spec) * self.env.dtype.itemsize
+        for extra in self.extra_cache_specs().values():
+            total += (context // extra.stride) * per_entry(extra) * self.env.dtype.itemsize
+        state = self.state_spec()
+        if state is not None:
+            total += 2 * 4 * per_entry(state)
+        return total
+
     def extra_cache_specs(self) -> Dict[str, PagedCacheSpec]:
         """Paged caches beside the main one (``cache_spec``), by name: pooled entries, for instance, of which
         there is one per block of positions.  The mixer finds them in ``cache.more[name]``."""
