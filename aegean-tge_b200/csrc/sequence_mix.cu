@@ -1,7 +1,12 @@
 // Kernels of the mixers that carry a fixed-size state from token to token, and of the layers around them:
 //
 //  * decay_scan       - linear attention with a fixed decay per head: S_t = c S_(t-1) + k_t v_t^T, o_t = S_t^T q_t,
-//                       the state in float32 in a per-request slot, q and k activated, rotated and scaled on the way in;
+//                       the state in float32 in a per-request slot, q and k activated, rotated and scaled on the way in.
+//                       Three kernels, chosen by the longest portion of a step: token by token (single tokens, short
+//                       portions), chunks of 32 tokens (any key size up to 256), chunks of 64 with register tiles and
+//                       asynchronous copies (keys up to 128), the last also in segments that share one long portion out
+//                       over the device (decay_segment_carry between its two launches); decay_prepare readies q and k
+//                       once per step for the chunked ones;
 //  * gated_norm       - RMS norm over groups of a row (a head, or all heads together), times an activated gate;
 //  * conv_norm_rope_store / conv_state_update - a short causal convolution over time on every channel of q, k and v
 //                       (its last taps-1 inputs kept per request), the per-head norm of q and k, their rotation, and
