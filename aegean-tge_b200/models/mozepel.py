@@ -11,7 +11,7 @@ logistic gate.  The feed-forward is SwiGLU.  A layer with ``weights_of`` runs an
 cache and state of its own (``LayerSpec.weights_from``).
 
 Checkpoint tensor names: ``embed``, ``final.norm``, ``head``, and per layer i ``l<i>.norm1``, ``l<i>.norm2``,
-``l<i>.mlp.{gate,up,down}``; retention ``l<i>.mix.{q,k,v,g,o}``; parallel ``l<i>.mix.left.{q,k,v,o}``,
+``l<i>.mlp.{gate,up,down}`` (a layer without feed-forward has neither these nor, as a rule, ``norm2``); retention ``l<i>.mix.{q,k,v,g,o}``; parallel ``l<i>.mix.left.{q,k,v,o}``,
 ``l<i>.mix.left.{q,k}.norm``, ``l<i>.mix.left.{q,k,v}.conv``, ``l<i>.mix.right.{q,k,v,g,o,norm}``.
 """
 from __future__ import annotations
@@ -74,7 +74,10 @@ def build_spec(config: MozepelConfig) -> ModelSpec:
             weights.update({f"right.{k}": v for k, v in right_w.items()})
             mixer = PartSpec("mixer_sum", {"branches": (("left", left, layer.mixer.left_scale),
                                                         ("right", right, layer.mixer.right_scale))}, weights)
-        ffn = norm2 = None
+        ffn = None
+        # a layer without feed-forward has no second sum to normalise; should a checkpoint hold a second norm for it
+        # all the same, it is applied to the scaled stream alone
+        norm2 = PartSpec("rmsnorm", {"size": width, "eps": eps, "optional": True}, {"weight": prefix + "norm2"})
         if layer.ff is not None:
             ffn = PartSpec("swiglu", {"hidden_size": width, "intermediate_size": layer.ff},
                            {"gate.weight": prefix + "mlp.gate", "up.weight": prefix + "mlp.up",

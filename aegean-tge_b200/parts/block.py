@@ -124,18 +124,16 @@ class PostNormBlock(Block):
     """x <- norm1(a x + mixer(x)); x <- norm2(a x + ffn(x)): the norm comes after the sum, and the sublayers
     read the stream itself.
 
-    params: ``alpha`` (a, default 1).  The feed-forward and its norm may be absent.  The stream stays float32; the
+    params: ``alpha`` (a, default 1).  The feed-forward and its norm may be absent; a second norm without a feed-forward
+    (a checkpoint that holds one for such a layer) normalises ``a x`` alone.  The stream stays float32; the
     kernel that normalises it also writes the rows the next product reads, so a sublayer's input is never normed
     on its own.  ``forward`` returns those rows for the next layer.
     """
 
     def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, env, params=None):
         super().__init__(mixer, feed_forward, mixer_norm, ffn_norm, env, params)
-        if (feed_forward is None) != (ffn_norm is None):
-            raise ValueError("post-norm block: a feed-forward and its norm come together")
-        for norm in (mixer_norm, ffn_norm):
-            if norm is not None and norm.fusable() is None:
-                raise ValueError("post-norm block: its norms are plain RMS norms")
+        if feed_forward is not None and ffn_norm is None:
+            raise ValueError("post-norm block: a feed-forward needs the norm that follows its sum")
         self.alpha = float(self.params.get("alpha", 1.0))
 
     def forward(self, x, ctx: StepContext, cache: LayerCache, h=None, next_norm=None):
@@ -144,7 +142,10 @@ class PostNormBlock(Block):
             h = ops.to_run_dtype(x, self.env.dtype)
         weight, eps = self.mixer_norm.fusable()
         h = ops.scale_add_norm(x, self.mixer.forward_f32(h, ctx, cache), self.alpha, weight, eps, self.env.dtype)
+        second = self.ffn_norm.fusable() if self.ffn_norm is not None else None
         if self.feed_forward is not None:
-            weight, eps = self.ffn_norm.fusable()
+            weight, eps = second
             h = ops.scale_add_norm(x, self.feed_forward.forward_f32(h, ctx), self.alpha, weight, eps, self.env.dtype)
+        elif second is not None:
+            h = ops.scale_add_norm(x, torch.zeros_like(x), self.alpha, second[0], second[1], self.env.dtype)
         return h

@@ -16,7 +16,8 @@ from .base import NORMS, Norm, ParamSpec
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``size`` (row width), ``eps``.  weights: ``weight``."""
+    """params: ``size`` (row width), ``eps``; optional ``optional`` (bool: a checkpoint may lack the weight; the norm
+    then does not exist: ``fusable()`` is None and ``forward`` refuses).  weights: ``weight``."""
     graph_safe = True
 
     def __init__(self, spec, env):
@@ -25,16 +26,23 @@ class RMSNorm(Norm):
         self.eps = float(spec.params["eps"])
         if self.size <= 0 or not self.eps > 0.0:
             raise ValueError(f"rmsnorm: size {self.size} and eps {self.eps} must be positive")
+        self.optional = bool(spec.params.get("optional", False))
+        self.loaded = False
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), role="vector")}
+        return {"weight": ParamSpec((self.size,), role="vector", optional=self.optional)}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"]
+        self.weight = tensors.get("weight") if self.optional else tensors["weight"]
+        self.loaded = True
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.weight is None:
+            raise RuntimeError("rmsnorm: the checkpoint holds no weight for this norm")
         return self.ops.rmsnorm(x, self.weight, self.eps, self.env.dtype, rows=rows)
 
     def fusable(self):
+        if self.optional and self.loaded and self.weight is None:
+            return None
         return self.weight, self.eps

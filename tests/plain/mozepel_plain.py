@@ -182,6 +182,8 @@ def layer_forward(x: np.ndarray, w: Dict[str, np.ndarray], config: dict, index: 
     x = rms_norm(alpha * x + mix(x, w, p + "mix.", entry["mixer"], eps), w[p + "norm1"], eps)
     if entry.get("mlp") is not None:
         x = rms_norm(alpha * x + gated_mlp(x, w[p + "mlp.gate"], w[p + "mlp.up"], w[p + "mlp.down"]), w[p + "norm2"], eps)
+    elif p + "norm2" in w:           # a second norm kept for a layer without feed-forward: of the scaled stream alone
+        x = rms_norm(alpha * x, w[p + "norm2"], eps)
     return x
 
 

@@ -508,6 +508,31 @@ def test_whole_prompts_and_first_tokens(folders, oracle, ops, name, dtype):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_second_norm_kept_for_a_layer_without_feed_forward(folders, tmp_path, dtype):
+    """A checkpoint may hold a second norm for a layer that has no feed-forward: it is then applied to the scaled
+    stream alone.  (Without the tensor the layer has one norm, as in every other test of configuration A.)"""
+    import shutil
+    from aegean_tge_b200.weights.safetensors_io import write_safetensors
+    weights = _read_weights(folders["A"])
+    assert "l2.norm2" not in weights and CONFIGS["A"]["layers"][2]["mlp"] is None
+    weights["l2.norm2"] = (1.0 + 0.3 * np.cos(np.arange(CONFIGS["A"]["width"]))).astype("<f4")
+    folder = tmp_path / "with_norm2"
+    folder.mkdir()
+    shutil.copy(os.path.join(folders["A"], "config.json"), folder / "config.json")
+    write_safetensors(str(folder / "model.safetensors"), {k: torch.from_numpy(v.copy()) for k, v in weights.items()})
+    tokens = _tokens("A", 70, salt=8)
+    w = weights if dtype == "float32" else {k: (_to_bfloat16(v) if v.ndim == 2 and not k.endswith(".conv") else v) for k, v in weights.items()}
+    ref = torch.from_numpy(plain.forward(CONFIGS["A"], w, tokens)).float()
+    without = {k: v for k, v in w.items() if k != "l2.norm2"}
+    assert rel_error(torch.from_numpy(plain.forward(CONFIGS["A"], without, tokens)).float(), ref) > 20 * MODEL_TOL["float32"]
+    from aegean_tge_b200 import Engine
+    engine = Engine(str(folder), dtype=dtype, context=256, max_tokens=512, max_requests=4)
+    rows = [engine.runner.step([_portion("r", tokens[:50])])]
+    rows += [engine.runner.step([_portion("r", tokens[t:t + 1])]) for t in range(50, 70)]
+    assert rel_error(torch.cat(rows), ref) < _tol("A", dtype)
+
+
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_each_mechanism_left_out_would_show(oracle, name):
     """The oracle with a window or block one off, without the convolution, with other branch scales, another alpha or
