@@ -3,7 +3,7 @@
 First every mechanism alone through its kernel (the decayed state with its rotation and activation, the gated norms,
 the short convolution with its per-request tail, the per-head norm and rotation before the store, pooled blocks and
 the window in one softmax, the norm after the sum), with inputs made so that a key one place off, a block seen too
-early or a lost state shows; then whole models of five small configurations that differ in every size, order and
+early or a lost state shows; then whole models of six small configurations that differ in every size, order and
 option, cut and batched in every way, both number formats.
 """
 import copy
@@ -41,8 +41,10 @@ def _rot(base, dims, scaling=None):
 
 
 def _retention(heads, dim, vdim, decay, rot, ff, weights_of=None):
-    entry = {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay, "rot": rot},
+    entry = {"type": "retention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "decay": decay},
              "mlp": None if ff is None else {"kind": "dense", "ff": ff}}
+    if rot is not None:
+        entry["mixer"]["rot"] = rot
     if weights_of is not None:
         entry["weights_of"] = weights_of
     return entry
@@ -57,8 +59,11 @@ def _parallel(left, right, left_scale, right_scale, ff, weights_of=None):
 
 
 def _left(heads, kv_heads, dim, vdim, scale, conv, size, pool, rot):
-    out = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": size, "pool": pool},
-           "rot": rot}
+    out = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale, "mask": {"size": size}}
+    if pool:
+        out["mask"]["pool"] = pool
+    if rot is not None:
+        out["rot"] = rot
     if conv:
         out["conv"] = conv
     return out
@@ -97,11 +102,14 @@ def _configs():
         # a window and blocks longer than the prompts of most tests: nothing is pooled until late
         "E": _config(150, 48, 1e-5, 1.5, [_parallel(_left(2, 1, 16, 16, 0.25, 4, 130, 64, _rot(1000.0, 8)),
                                                     _right(2, 8, 8, [0.5, 0.9]), 0.5, 2.0, None)]),
+        # what a model may leave out: no rotation anywhere, no convolution, a window without pooled blocks
+        "F": _config(180, 80, 1e-5, 1.2, [_retention(2, 16, 24, [0.93, 0.99], None, 48),
+                                          _parallel(_left(4, 2, 16, 32, 0.25, 0, 20, 0, None), _right(2, 16, 16, [0.8, 0.97]), 0.9, 1.1, 64)]),
     }
 
 
 CONFIGS = _configs()
-SEEDS = {"A": 21, "B": 22, "C": 23, "D": 24, "E": 25}
+SEEDS = {"A": 21, "B": 22, "C": 23, "D": 24, "E": 25, "F": 26}
 
 
 @pytest.fixture(scope="module")
